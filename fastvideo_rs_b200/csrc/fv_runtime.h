@@ -1,0 +1,31 @@
+// Host-side runtime shared by the entry points: thread-local error text,
+// device capability check, the per-device kernel status word, and the
+// cuTensorMapEncodeTiled entry obtained from the driver at run time (the
+// library links against cudart only).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include "../../include/fv_sdpa.h"
+
+namespace fvrt {
+
+int fail(int code, const char* fmt, ...);   // sets the error text, returns code
+void clear_error();
+// FV_RAN when the current device is sm_100 / sm_103; else FV_ERR_NO_DEVICE (text set).
+int require_sm100(int* device_out);
+// Device pointer of the current device's status word (allocated and zeroed on first use).
+int status_word(int device, int** ptr_out);
+
+// 4-D bf16 tensor map, dims innermost first, strides in bytes for dims 1..3,
+// box (64, box_rows, 1, 1), 128-byte swizzle, out-of-range reads as zero.
+int encode_map4(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint64_t strides[3],
+                uint32_t box_rows);
+
+#define FV_CUDA(expr)                                                                           \
+    do {                                                                                        \
+        cudaError_t e__ = (expr);                                                               \
+        if (e__ != cudaSuccess) return fvrt::fail(FV_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e__)); \
+    } while (0)
+
+}  // namespace fvrt

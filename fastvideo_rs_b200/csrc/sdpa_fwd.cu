@@ -1,0 +1,122 @@
+// Entry kernels and host launcher of the head-dim-128 SDPA forward.
+#include "sdpa_fwd.cuh"
+#include "fv_runtime.h"
+#include <math.h>
+
+namespace fvsdpa {
+
+constexpr int kStages = 4;
+
+__global__ void __launch_bounds__(kThreads, 1)
+fv_sdpa_fwd_d128(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                 const __grid_constant__ CUtensorMap tv, const __grid_constant__ Params p) {
+#if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL)
+    extern __shared__ __align__(1024) unsigned char fv_smem[];
+    sdpa_body<kStages>(&tq, &tk, &tv, p, fv_smem);
+#endif
+}
+
+static int launch(cudaStream_t stream, const void* q, const void* k, const void* v, void* out, int out_is_bf16, int bh,
+                  int sq, int nseg, const int* seg_len, const int* seg_start, int seg_rows, float scale, int mask_mode,
+                  int block_tokens, int window, int sink, int q_row0, float* lse_out, const float* prev_o,
+                  const float* prev_lse) {
+    int dev;
+    int rc = fvrt::require_sm100(&dev);
+    if (rc != FV_RAN) return rc;
+    if (!q || !k || !v || !out) return fvrt::fail(FV_ERR_INVALID, "sdpa: null operand");
+    if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15)
+        return fvrt::fail(FV_ERR_INVALID, "sdpa: operands must be 16-byte aligned");
+    if ((prev_o == nullptr) != (prev_lse == nullptr))
+        return fvrt::fail(FV_ERR_INVALID, "sdpa: prev_o and prev_lse go together");
+    if (prev_o && ((uintptr_t)prev_o & 15)) return fvrt::fail(FV_ERR_INVALID, "sdpa: prev_o must be 16-byte aligned");
+    if (!(scale > 0.f) || !isfinite(scale)) return fvrt::fail(FV_ERR_INVALID, "sdpa: scale must be positive and finite");
+    if (mask_mode != FV_MASK_NONE && mask_mode != FV_MASK_BLOCK_CAUSAL)
+        return fvrt::fail(FV_ERR_INVALID, "sdpa: unknown mask mode %d", mask_mode);
+    if (mask_mode == FV_MASK_BLOCK_CAUSAL && (block_tokens < 1 || window < 0 || sink < 0 || q_row0 < 0))
+        return fvrt::fail(FV_ERR_INVALID, "sdpa: block-causal needs block_tokens >= 1, window, sink, q_row0 >= 0");
+    if (nseg < 1 || nseg > kMaxSeg) return fvrt::fail(FV_ERR_INVALID, "sdpa: 1..%d K/V segments", kMaxSeg);
+
+    Params p{};
+    p.out = out;
+    p.lse_out = lse_out;
+    p.prev_o = prev_o;
+    p.prev_lse = prev_lse;
+    p.out_is_bf16 = out_is_bf16 ? 1 : 0;
+    p.bh = bh;
+    p.sq = sq;
+    p.nqb = (sq + kRowsPerCta - 1) / kRowsPerCta;
+    p.sl2 = scale * 1.4426950408889634f;
+    p.nseg = nseg;
+    long long total = 0;
+    for (int s = 0; s < nseg; s++) {
+        if (seg_len[s] < 0 || seg_len[s] > seg_rows || seg_start[s] < 0)
+            return fvrt::fail(FV_ERR_INVALID, "sdpa: segment %d has length %d (rows %d), start %d", s, seg_len[s], seg_rows,
+                              seg_start[s]);
+        p.seg_len[s] = seg_len[s];
+        p.seg_start[s] = seg_start[s];
+        total += seg_len[s];
+        if ((long long)seg_start[s] + seg_len[s] > 0x3fffffffll) return FV_DECLINED;
+    }
+    if (total == 0) return FV_DECLINED;
+    p.mask_mode = mask_mode;
+    p.block_tokens = block_tokens;
+    p.window = window;
+    p.sink = sink;
+    p.q_row0 = q_row0;
+    p.heavy_first = mask_mode == FV_MASK_BLOCK_CAUSAL;
+    rc = fvrt::status_word(dev, &p.status);
+    if (rc != FV_RAN) return rc;
+
+    const long long grid = (long long)p.nqb * bh;
+    if (grid > 0x7fffffffll) return FV_DECLINED;
+
+    CUtensorMap tq, tk, tv;
+    {
+        const uint64_t dq[4] = {128, (uint64_t)sq, (uint64_t)bh, 1};
+        const uint64_t sqb[3] = {256, (uint64_t)sq * 256, (uint64_t)sq * 256 * bh};
+        rc = fvrt::encode_map4(&tq, q, dq, sqb, 128);
+        if (rc != FV_RAN) return rc;
+        const uint64_t dk[4] = {128, (uint64_t)seg_rows, (uint64_t)bh, (uint64_t)nseg};
+        const uint64_t skb[3] = {256, (uint64_t)seg_rows * 256, (uint64_t)seg_rows * 256 * bh};
+        rc = fvrt::encode_map4(&tk, k, dk, skb, 128);
+        if (rc != FV_RAN) return rc;
+        rc = fvrt::encode_map4(&tv, v, dk, skb, 128);
+        if (rc != FV_RAN) return rc;
+    }
+
+    static bool attr_set[64] = {};
+    constexpr uint32_t smem = smem_bytes<kStages>();
+    if (!attr_set[dev]) {
+        FV_CUDA(cudaFuncSetAttribute(fv_sdpa_fwd_d128, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[dev] = true;
+    }
+    fv_sdpa_fwd_d128<<<(unsigned)grid, kThreads, smem, stream>>>(tq, tk, tv, p);
+    FV_CUDA(cudaGetLastError());
+    return FV_RAN;
+}
+
+}  // namespace fvsdpa
+
+extern "C" int fv_sdpa_segments_bf16(void* stream, const void* q, const void* k, const void* v, void* out,
+                                     int out_is_bf16, int bh, int sq, int nseg, const int* seg_len,
+                                     const int* seg_start, int seg_rows, float scale, int mask_mode, int block_tokens,
+                                     int window, int sink, int q_row0, float* lse_out, const float* prev_o,
+                                     const float* prev_lse) {
+    fvrt::clear_error();
+    if (bh <= 0 || sq <= 0 || nseg <= 0 || seg_rows <= 0) return FV_DECLINED;
+    if (sq > 0x3fffffff || seg_rows > 0x3fffffff) return FV_DECLINED;
+    if (!seg_len || !seg_start) return fvrt::fail(FV_ERR_INVALID, "sdpa: null segment table");
+    return fvsdpa::launch((cudaStream_t)stream, q, k, v, out, out_is_bf16, bh, sq, nseg, seg_len, seg_start, seg_rows,
+                          scale, mask_mode, block_tokens, window, sink, q_row0, lse_out, prev_o, prev_lse);
+}
+
+extern "C" int fv_sdpa_dense_bf16(void* stream, const void* q, const void* k, const void* v, void* out, int out_is_bf16,
+                                  int bh, int sq, int sk, int d, float scale, int mask_mode, int block_tokens,
+                                  int window, int sink, int q_row0) {
+    fvrt::clear_error();
+    if (d != 128 || bh <= 0 || sq <= 0 || sk <= 0) return FV_DECLINED;
+    if (sq > 0x3fffffff || sk > 0x3fffffff) return FV_DECLINED;
+    const int len = sk, start = 0;
+    return fvsdpa::launch((cudaStream_t)stream, q, k, v, out, out_is_bf16, bh, sq, 1, &len, &start, sk, scale, mask_mode,
+                          block_tokens, window, sink, q_row0, nullptr, nullptr, nullptr);
+}

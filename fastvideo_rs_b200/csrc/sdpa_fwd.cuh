@@ -1,0 +1,457 @@
+// Flash-style SDPA forward for head dim 128 on sm_100a: TMA-staged Q/K/V,
+// tcgen05.mma (cta_group::1, kind::f16) with TMEM accumulators, one query row
+// per softmax thread.  One kernel body serves dense self/cross attention, the
+// Wan block-causal mask, sequence-parallel K/V (several gathered segments) and
+// the second pass of a two-pass (local keys, then remote keys) evaluation.
+//
+// Replaces, behind the same operand convention (bf16 [bh, s, 128] in, bf16 or
+// f32 [bh, sq, 128] out, sl2 = scale * log2 e), the reference launcher
+// crates/fastvideo-cudarc/src/rt/attn_dc.rs:213-273 (dense_fwd) and the
+// block-causal launcher crates/fastvideo-cudarc/src/rt/attn.rs:647-730.
+//
+// CTA = 256 query rows of one head = two M=128 query tiles; 12 warps:
+//   warps 0-3 / 4-7  softmax of query tile 0 / 1 (thread = TMEM lane = row)
+//   warp 8           TMA producer (one thread)
+//   warp 9           tcgen05.mma issuer (one thread); owns TMEM alloc/dealloc
+//   warps 10-11      idle (they keep warpgroup 2 whole for setmaxnreg)
+// TMEM, 512 columns: S0 | S1 | O0 | O1 (128 f32 columns each); the bf16
+// probabilities P_i overwrite columns 0-63 of S_i and feed the P.V MMA from
+// TMEM.  MMA issue order per visited key tile j: PV0(j-1) QK0(j) PV1(j-1)
+// QK1(j), so one tile's softmax runs under the other tile's MMAs.
+//
+// Softmax: base-2 domain, running reference max m advanced LAZILY (only when
+// the tile max exceeds m by more than 8, i.e. a factor 256 of headroom in P),
+// so O in TMEM is rescaled a handful of times per row instead of every tile;
+// the result is mathematically identical because O and l share the reference.
+#pragma once
+#include <cuda.h>
+#include "fv_ptx.cuh"
+
+namespace fvsdpa {
+
+constexpr int kD = 128;
+constexpr int kBN = 128;              // keys per tile
+constexpr int kRowsPerCta = 256;
+constexpr uint32_t kPanelB = 16384;   // 128 rows x 64 bf16, one swizzled TMA box
+constexpr uint32_t kTileB = 32768;    // 128 x 128 bf16 = two panels
+constexpr int kMaxSeg = 8;
+constexpr int kThreads = 384;
+constexpr float kLazyLog2 = 8.0f;
+
+template <int NS>
+constexpr uint32_t smem_bytes() {
+    return 1024u + 2u * kTileB + (uint32_t)NS * kTileB + 256u;
+}
+
+struct Params {
+    void* out;              // [bh, sq, 128] bf16 or f32
+    float* lse_out;         // optional [bh, sq]: m + log2(l) in the base-2 domain, -inf for an empty row
+    const float* prev_o;    // optional f32 [bh, sq, 128]: normalised result of an earlier pass over other keys
+    const float* prev_lse;  // its lse (same convention); both or neither
+    int* status;            // device status word (0 = fine)
+    int out_is_bf16;
+    int bh, sq, nqb;
+    float sl2;
+    int nseg;
+    int seg_len[kMaxSeg];    // keys in each K/V segment
+    int seg_start[kMaxSeg];  // global key index of the segment's first key
+    int mask_mode;           // 0 = none, 1 = block causal
+    int block_tokens, window, sink;
+    int q_row0;              // global index of query row 0 (sequence-parallel shard offset)
+    int heavy_first;         // walk query blocks from the last to the first
+};
+
+#if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL) || !defined(__CUDA_ARCH__)
+
+FV_DEV int sat_mul(int a, int b) {
+    long long v = (long long)a * (long long)b;
+    return v > 0x7fffffffll ? 0x7fffffff : (int)v;
+}
+
+// The key tiles a CTA visits, identical in every role.  f(seg, t, k0, lim):
+// segment, tile index inside it, global index of column 0, valid columns.
+template <class F>
+FV_DEV void walk_tiles(const Params& p, int vis_lo, int vis_hi, int vis_sink, F&& f) {
+    for (int seg = 0; seg < p.nseg; seg++) {
+        const int len = p.seg_len[seg], start = p.seg_start[seg];
+        const int nt = (len + kBN - 1) / kBN;
+        for (int t = 0; t < nt; t++) {
+            const int k0 = start + t * kBN;
+            const int lim = min(kBN, len - t * kBN);
+            if (p.mask_mode) {
+                const int k1 = k0 + lim;
+                if (!((k0 < vis_hi && k1 > vis_lo) || k0 < vis_sink)) continue;
+            }
+            if (!f(seg, t, k0, lim)) return;
+        }
+    }
+}
+
+// S (TMEM 128 x 128 f32) = Q (128 x 128, K-major SW128) . K^T (128 keys, K-major SW128)
+FV_DEV void issue_qk(uint32_t tS, uint32_t sQ, uint32_t sK) {
+    constexpr uint32_t idesc = fvp::umma_idesc_bf16(128, 128, 0);
+#pragma unroll
+    for (int kk = 0; kk < 8; kk++) {
+        const uint32_t off = (uint32_t)(kk >> 2) * kPanelB + (uint32_t)(kk & 3) * 32u;
+        fvp::umma_ss(tS, fvp::umma_desc_sw128(sQ + off, 16, 1024), fvp::umma_desc_sw128(sK + off, 16, 1024), idesc,
+                     kk > 0);
+    }
+}
+// O (TMEM 128 x 128 f32) (+)= P (TMEM bf16, 128 rows x 128 keys) . V (128 keys x 128, MN-major:
+// 64-column panels kPanelB apart, 8-key groups 1024 B apart)
+FV_DEV void issue_pv(uint32_t tO, uint32_t tP, uint32_t sV, bool acc) {
+    constexpr uint32_t idesc = fvp::umma_idesc_bf16(128, 128, 1);
+#pragma unroll
+    for (int kk = 0; kk < 8; kk++) {
+        fvp::umma_ts(tO, tP + 8u * kk, fvp::umma_desc_sw128(sV + 2048u * kk, kPanelB, 1024), idesc, acc || kk > 0);
+    }
+}
+
+FV_DEV float u2f(uint32_t u) { return __uint_as_float(u); }
+FV_DEV uint32_t f2u(float f) { return __float_as_uint(f); }
+
+template <int NS>
+FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtensorMap* tv, const Params& p,
+                      unsigned char* smem_raw) {
+    using namespace fvp;
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const uint32_t sQ = base;
+    const uint32_t ring = base + 2 * kTileB;
+    const uint32_t bars = ring + NS * kTileB;
+    const uint32_t b_q = bars;
+    const uint32_t b_full = b_q + 8;
+    const uint32_t b_empty = b_full + 8 * NS;
+    const uint32_t b_s = b_empty + 8 * NS;
+    const uint32_t b_p = b_s + 16;
+    const uint32_t b_o = b_p + 16;
+    const uint32_t b_drain = b_o + 16;
+    const uint32_t tslot = b_drain + 8;
+    const uint32_t aflag = tslot + 4;
+    volatile uint32_t* tslot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tslot - raw));
+    volatile int* abort_ptr = reinterpret_cast<volatile int*>(smem_raw + (aflag - raw));
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int qb = (int)(blockIdx.x % (unsigned)p.nqb);
+    const int bh = (int)(blockIdx.x / (unsigned)p.nqb);
+    if (p.heavy_first) qb = p.nqb - 1 - qb;
+    const int q0 = qb * kRowsPerCta;
+    const float NEG = __int_as_float(0xff800000);
+
+    if (tid == 0) {
+        mbar_init(b_q, 1);
+        for (int i = 0; i < NS; i++) {
+            mbar_init(b_full + 8 * i, 1);
+            mbar_init(b_empty + 8 * i, 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(b_s + 8 * i, 1);
+            mbar_init(b_p + 8 * i, 128);
+            mbar_init(b_o + 8 * i, 1);
+        }
+        mbar_init(b_drain, 1);
+        // A CTA that starts after another one gave up does nothing.
+        *abort_ptr = (*(volatile int*)p.status != FV_ST_OK) ? 1 : 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+    if (*abort_ptr) return;  // CTA-uniform
+    if (warp == 9) tmem_alloc(tslot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tbase = *tslot_ptr;
+
+    // Keys any row of this CTA may see (block-causal): [vis_lo, vis_hi) U [0, vis_sink).
+    int vis_lo = 0, vis_hi = 0x7fffffff, vis_sink = 0;
+    const int bt = max(p.block_tokens, 1);
+    if (p.mask_mode) {
+        const int qg_min = p.q_row0 + q0;
+        const int qg_max = p.q_row0 + min(q0 + kRowsPerCta - 1, p.sq - 1);
+        const int tq_min = qg_min / bt, tq_max = qg_max / bt;
+        vis_hi = sat_mul(tq_max + 1, bt);
+        vis_lo = p.window > 0 ? sat_mul(max(0, tq_min - p.window + 1), bt) : 0;
+        vis_sink = sat_mul(p.sink, bt);
+    }
+
+    if (warp < 8) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
+        // ------------------------------------------------------------ softmax
+        WaitCtl ctl{abort_ptr, p.status, 3};
+        const int tile = warp >> 2, sub = warp & 3;
+        const int row = sub * 32 + lane;
+        const uint32_t tl = tbase + ((uint32_t)(sub * 32) << 16);
+        const uint32_t tS = tl + 128u * tile, tP = tS, tO = tl + 256u + 128u * tile;
+        const int qr = q0 + 128 * tile + row;
+        // Keys this row may see: [r_lo, r_hi) U [0, r_sink).
+        int r_lo = 0, r_hi = 0x7fffffff, r_sink = 0;
+        if (p.mask_mode) {
+            const int tqr = (p.q_row0 + qr) / bt;
+            r_hi = sat_mul(tqr + 1, bt);
+            r_lo = p.window > 0 ? sat_mul(max(0, tqr - p.window + 1), bt) : 0;
+            r_sink = vis_sink;
+        }
+        const float sl2 = p.sl2;
+        float m = NEG, l = 0.f;
+        int it = 0;
+        bool ok = true;
+        walk_tiles(p, vis_lo, vis_hi, vis_sink, [&](int, int, int k0, int lim) -> bool {
+            // Warp-uniform outcome: the TMEM instructions below are warp-collective.
+            if (!__all_sync(0xffffffffu, mbar_wait(b_s + 8 * tile, it & 1, ctl))) { ok = false; return false; }
+            tc_fence_after();
+            uint32_t u[128];
+            tmem_ld32_issue<0>(tS, u);
+            tmem_ld32_issue<32>(tS + 32u, u);
+            tmem_ld32_issue<64>(tS + 64u, u);
+            tmem_ld32_issue<96>(tS + 96u, u);
+            tmem_ld_wait();
+            tmem_pin(u);
+            // Visible columns of this row in this tile: [c_lo, c_hi) U [0, c_sink).
+            const int c_lo = min(max(r_lo - k0, 0), lim);
+            const int c_hi = min(max(r_hi - k0, 0), lim);
+            const int c_sink = min(max(r_sink - k0, 0), lim);
+            if (!((c_lo == 0 && c_hi == kBN) || c_sink == kBN)) {
+#pragma unroll
+                for (int c = 0; c < 128; c++) {
+                    const bool vis = (c >= c_lo && c < c_hi) || c < c_sink;
+                    u[c] = vis ? u[c] : f2u(NEG);
+                }
+            }
+            float x0 = u2f(u[0]), x1 = u2f(u[1]), x2 = u2f(u[2]), x3 = u2f(u[3]);
+#pragma unroll
+            for (int c = 4; c < 128; c += 4) {
+                x0 = fmaxf(x0, u2f(u[c]));
+                x1 = fmaxf(x1, u2f(u[c + 1]));
+                x2 = fmaxf(x2, u2f(u[c + 2]));
+                x3 = fmaxf(x3, u2f(u[c + 3]));
+            }
+            const float tm2 = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3)) * sl2;
+            const bool grow = tm2 > m + kLazyLog2;
+            float a = 1.f;
+            if (grow) {
+                a = ex2(m - tm2);
+                m = tm2;
+            }
+            const float off = (m == NEG) ? 0.f : m;
+            // O holds P.V of the tiles before this one (its MMA finished before
+            // this S did): rescale it when a row of the warp moved its reference.
+            if (it > 0 && __any_sync(0xffffffffu, grow)) {
+#pragma unroll 1
+                for (int q = 0; q < 4; q++) {
+                    uint32_t o[32];
+                    tmem_ld32_issue(tO + 32u * q, o);
+                    tmem_ld_wait();
+                    tmem_pin(o);
+#pragma unroll
+                    for (int c = 0; c < 32; c++) o[c] = f2u(u2f(o[c]) * a);
+                    tmem_st32(tO + 32u * q, o);
+                }
+            }
+            float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                uint32_t pw[32];
+#pragma unroll
+                for (int w = 0; w < 32; w += 2) {
+                    const float p0 = ex2(fmaf(u2f(u[64 * h + 2 * w]), sl2, -off));
+                    const float p1 = ex2(fmaf(u2f(u[64 * h + 2 * w + 1]), sl2, -off));
+                    const float p2 = ex2(fmaf(u2f(u[64 * h + 2 * w + 2]), sl2, -off));
+                    const float p3 = ex2(fmaf(u2f(u[64 * h + 2 * w + 3]), sl2, -off));
+                    y0 += p0;
+                    y1 += p1;
+                    y2 += p2;
+                    y3 += p3;
+                    pw[w] = pack_bf16x2(p0, p1);
+                    pw[w + 1] = pack_bf16x2(p2, p3);
+                }
+                tmem_st32(tP + 32u * h, pw);
+            }
+            l = fmaf(l, a, (y0 + y1) + (y2 + y3));
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(b_p + 8 * tile);
+            it++;
+            return true;
+        });
+
+        // ----------------------------------------------------------- epilogue
+        if (ok && it > 0) ok = __all_sync(0xffffffffu, mbar_wait(b_o + 8 * tile, 0, ctl));
+        tc_fence_after();
+        if (ok) {
+            const bool live = qr < p.sq;  // rows past sq take part in the warp-collective TMEM loads only
+            float inv = l > 0.f ? 1.f / l : 0.f;
+            const float lse = l > 0.f ? m + log2f(l) : NEG;
+            const size_t rowi = (size_t)bh * p.sq + (live ? qr : 0);
+            float cp = 0.f;  // weight of the earlier pass
+            if (live) {
+                if (p.prev_o) {
+                    const float pl = p.prev_lse[rowi];
+                    const float M = fmaxf(lse, pl);
+                    float lse_all = NEG;
+                    if (M != NEG) {
+                        const float wn = exp2f(lse - M), wp = exp2f(pl - M);
+                        const float den = 1.f / (wn + wp);
+                        inv *= wn * den;
+                        cp = wp * den;
+                        lse_all = M + log2f(wn + wp);
+                    }
+                    if (p.lse_out) p.lse_out[rowi] = lse_all;
+                } else if (p.lse_out) {
+                    p.lse_out[rowi] = lse;
+                }
+            }
+            const size_t off = rowi * kD;
+#pragma unroll 1
+            for (int q = 0; q < 4; q++) {
+                uint32_t o[32];
+                if (it > 0) {  // CTA-uniform
+                    tmem_ld32_issue(tO + 32u * q, o);
+                    tmem_ld_wait();
+                    tmem_pin(o);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; c++) o[c] = 0u;
+                }
+                if (!live) continue;
+                float f[32];
+#pragma unroll
+                for (int c = 0; c < 32; c++) f[c] = u2f(o[c]) * inv;
+                if (p.prev_o) {
+                    const float4* po = reinterpret_cast<const float4*>(p.prev_o + off + 32 * q);
+#pragma unroll
+                    for (int c = 0; c < 8; c++) {
+                        const float4 t = po[c];
+                        f[4 * c] = fmaf(t.x, cp, f[4 * c]);
+                        f[4 * c + 1] = fmaf(t.y, cp, f[4 * c + 1]);
+                        f[4 * c + 2] = fmaf(t.z, cp, f[4 * c + 2]);
+                        f[4 * c + 3] = fmaf(t.w, cp, f[4 * c + 3]);
+                    }
+                }
+                if (p.out_is_bf16) {
+                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.out) + off + 32 * q);
+#pragma unroll
+                    for (int c = 0; c < 4; c++)
+                        dst[c] = make_uint4(pack_bf16x2(f[8 * c], f[8 * c + 1]), pack_bf16x2(f[8 * c + 2], f[8 * c + 3]),
+                                            pack_bf16x2(f[8 * c + 4], f[8 * c + 5]), pack_bf16x2(f[8 * c + 6], f[8 * c + 7]));
+                } else {
+                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + off + 32 * q);
+#pragma unroll
+                    for (int c = 0; c < 8; c++) dst[c] = make_float4(f[4 * c], f[4 * c + 1], f[4 * c + 2], f[4 * c + 3]);
+                }
+            }
+        }
+        // Every TMEM access of this thread is complete: warp 9 may free the columns.
+        tc_fence_before();
+        asm volatile("bar.arrive 1, 288;" ::: "memory");
+        return;
+    }
+
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
+    if (warp == 8) {
+        // ------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            WaitCtl ctl{abort_ptr, p.status, 1};
+            tma_prefetch_desc(tq);
+            tma_prefetch_desc(tk);
+            tma_prefetch_desc(tv);
+            mbar_expect_tx(b_q, 2 * kTileB);
+            tma_load4(sQ, tq, b_q, 0, q0, bh, 0);
+            tma_load4(sQ + kPanelB, tq, b_q, 64, q0, bh, 0);
+            tma_load4(sQ + kTileB, tq, b_q, 0, q0 + 128, bh, 0);
+            tma_load4(sQ + kTileB + kPanelB, tq, b_q, 64, q0 + 128, bh, 0);
+            int idx = 0;
+            bool ok = true;
+            walk_tiles(p, vis_lo, vis_hi, vis_sink, [&](int seg, int t, int, int) -> bool {
+#pragma unroll 1
+                for (int half = 0; half < 2; half++) {
+                    const int slot = idx % NS, use = idx / NS;
+                    if (use > 0 && !mbar_wait(b_empty + 8 * slot, (use - 1) & 1, ctl)) { ok = false; return false; }
+                    const uint32_t dst = ring + slot * kTileB, bar = b_full + 8 * slot;
+                    const CUtensorMap* map = half ? tv : tk;
+                    mbar_expect_tx(bar, kTileB);
+                    tma_load4(dst, map, bar, 0, t * kBN, bh, seg);
+                    tma_load4(dst + kPanelB, map, bar, 64, t * kBN, bh, seg);
+                    idx++;
+                }
+                return true;
+            });
+            // Copies in flight must land before the CTA's shared memory goes away.  On the
+            // normal path the MMA thread has already waited on each of these phases.
+            mbar_wait(b_q, 0, ctl);
+            for (int s = 0; s < NS && s < idx; s++) {
+                const int last = ((idx - 1 - s) / NS) * NS + s;  // last load index that used slot s
+                mbar_wait(b_full + 8 * s, (last / NS) & 1, ctl);
+            }
+            (void)ok;
+        }
+        return;
+    }
+    if (warp == 9) {
+        // --------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            WaitCtl ctl{abort_ptr, p.status, 2};
+            // This role needs only the number of visited tiles, not which ones.
+            int nvis = 0;
+            walk_tiles(p, vis_lo, vis_hi, vis_sink, [&](int, int, int, int) -> bool { nvis++; return true; });
+            bool ok = mbar_wait(b_q, 0, ctl);
+            tc_fence_after();
+            int it = 0;
+#pragma unroll 1
+            for (; ok && it < nvis; it++) {
+                const int ik = 2 * it, slotK = ik % NS;
+                if (!mbar_wait(b_full + 8 * slotK, (ik / NS) & 1, ctl)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t sK = ring + slotK * kTileB;
+                if (it == 0) {
+                    issue_qk(tbase, sQ, sK);
+                    umma_commit(b_s);
+                    issue_qk(tbase + 128u, sQ + kTileB, sK);
+                    umma_commit(b_s + 8);
+                    umma_commit(b_empty + 8 * slotK);
+                } else {
+                    const int iv = ik - 1, slotV = iv % NS;
+                    if (!mbar_wait(b_full + 8 * slotV, (iv / NS) & 1, ctl)) { ok = false; break; }
+                    const uint32_t sV = ring + slotV * kTileB;
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        if (ok && !mbar_wait(b_p + 8 * i, (it - 1) & 1, ctl)) ok = false;
+                        if (ok) {
+                            tc_fence_after();
+                            issue_pv(tbase + 256u + 128u * i, tbase + 128u * i, sV, it > 1);
+                            issue_qk(tbase + 128u * i, sQ + i * kTileB, sK);
+                            umma_commit(b_s + 8 * i);
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit(b_empty + 8 * slotV);
+                    umma_commit(b_empty + 8 * slotK);
+                }
+            }
+            if (ok && it > 0) {
+                const int iv = 2 * it - 1, slotV = iv % NS;
+                ok = mbar_wait(b_full + 8 * slotV, (iv / NS) & 1, ctl);
+                const uint32_t sV = ring + slotV * kTileB;
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    if (ok) ok = mbar_wait(b_p + 8 * i, (it - 1) & 1, ctl);
+                    if (ok) {
+                        tc_fence_after();
+                        issue_pv(tbase + 256u + 128u * i, tbase + 128u * i, sV, it > 1);
+                        umma_commit(b_o + 8 * i);
+                    }
+                }
+            }
+            // Nothing this thread issued may still be running when TMEM is freed.
+            umma_commit(b_drain);
+            mbar_wait(b_drain, 0, ctl);
+        }
+        __syncwarp();
+        asm volatile("bar.sync 1, 288;" ::: "memory");
+        tc_fence_after();
+        tmem_dealloc(tbase, 512);
+    }
+}
+
+#endif  // sm_100a / host pass
+
+}  // namespace fvsdpa
