@@ -1,0 +1,182 @@
+// Wan q/k prologue: RMSNorm (statistic over the whole heads*d projection row, or per head),
+// weight, interleaved-pair 3-D RoPE, head split to BHSD bf16 -- one pass over the fused QKV
+// projection, V's head split riding along.  HBM-bound: reads each projection element once,
+// writes each output element once.
+//
+// Replaces the two qk_norm_rope_bhsd launches and the split_heads_bhsd launch of
+// WanAttention::forward_self (crates/fastvideo-cudarc/src/wan/transformer.rs:163-178,287-289;
+// kernels crates/fastvideo-cudarc/src/rt/kernels/core.cu:368-428).  Arithmetic follows the f32
+// host twin crates/fastvideo-cudarc/src/rt/ops.rs:2304-2350: inv = 1/sqrt(mean(x^2) + eps),
+// y = (x*inv)*w, even = y0*cos[s,even] - y1*sin[s,even+1], odd = y0*sin[s,even+1] + y1*cos[s,even],
+// every product and sum rounded separately (no fused multiply-add), then one rounding to bf16.
+// Only the order of the sum of squares differs (tree reduction instead of a sequential sum).
+#include "fv_runtime.h"
+#include <cuda_bf16.h>
+
+namespace fvprep {
+
+constexpr int kD = 128;
+
+struct Params {
+    const __nv_bfloat16* proj;  // [batch, seq, width]
+    const float* wq;            // [heads*128]
+    const float* wk;
+    const float* cosv;          // [seq, 128] or null (no rotation)
+    const float* sinv;
+    __nv_bfloat16* q_out;       // [batch*heads, seq, 128] (null: skip q)
+    __nv_bfloat16* k_out;
+    __nv_bfloat16* v_out;       // null: skip v
+    int batch, seq, heads, width, col_q, col_k, col_v;
+    float eps;
+    int per_head;
+};
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// One CTA per token row (b, s); thread t owns elements 8t..8t+7 of the heads*128 row, i.e.
+// 8 consecutive dims of head (8t)/128.  blockDim.x = heads*16.
+__global__ void __launch_bounds__(1024) fv_wan_qk_prep_kernel(const Params p) {
+    extern __shared__ float red[];  // [2][nwarps]
+    const int row = blockIdx.x;     // b*seq + s
+    const int b = row / p.seq, s = row % p.seq;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = blockDim.x >> 5;
+    const int h = (8 * t) / kD, pd = (8 * t) % kD;
+    const __nv_bfloat16* src = p.proj + (size_t)row * p.width;
+    const size_t dst = (((size_t)b * p.heads + h) * p.seq + s) * kD + pd;
+
+    if (p.v_out) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src + p.col_v + 8 * t);
+        *reinterpret_cast<uint4*>(p.v_out + dst) = v;
+    }
+    float xq[8], xk[8];
+    float sq = 0.f, sk = 0.f;
+    if (p.q_out) {
+        unpack8(*reinterpret_cast<const uint4*>(src + p.col_q + 8 * t), xq);
+#pragma unroll
+        for (int i = 0; i < 8; i++) sq = __fadd_rn(sq, __fmul_rn(xq[i], xq[i]));
+    }
+    if (p.k_out) {
+        unpack8(*reinterpret_cast<const uint4*>(src + p.col_k + 8 * t), xk);
+#pragma unroll
+        for (int i = 0; i < 8; i++) sk = __fadd_rn(sk, __fmul_rn(xk[i], xk[i]));
+    }
+    // Sum of squares: over the 16 threads of a head (per_head) or over the whole row.
+    const int span = p.per_head ? 16 : 32;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        if (o < span) {
+            sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            sk += __shfl_xor_sync(0xffffffffu, sk, o);
+        }
+    }
+    float denom = (float)kD;
+    if (!p.per_head) {
+        if (lane == 0) {
+            red[warp] = sq;
+            red[nwarps + warp] = sk;
+        }
+        __syncthreads();
+        float a = 0.f, c = 0.f;
+        for (int w = 0; w < nwarps; w++) {
+            a += red[w];
+            c += red[nwarps + w];
+        }
+        sq = a;
+        sk = c;
+        denom = (float)(p.heads * kD);
+    }
+    float cs[8], sn[8];
+    if (p.cosv) {
+        const float4* cp = reinterpret_cast<const float4*>(p.cosv + (size_t)s * kD + pd);
+        const float4* sp = reinterpret_cast<const float4*>(p.sinv + (size_t)s * kD + pd);
+        const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+        cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+        sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    }
+    auto finish = [&](const float (&x)[8], float ss, const float* w, __nv_bfloat16* out) {
+        const float ms = __fdiv_rn(ss, denom);
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, p.eps)));
+        const float4 w0 = *reinterpret_cast<const float4*>(w + 8 * t), w1 = *reinterpret_cast<const float4*>(w + 8 * t + 4);
+        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) y[i] = __fmul_rn(__fmul_rn(x[i], inv), wv[i]);
+        float o[8];
+        if (p.cosv) {
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) {
+                const float c = cs[i], sv = sn[i + 1];
+                o[i] = __fsub_rn(__fmul_rn(y[i], c), __fmul_rn(y[i + 1], sv));
+                o[i + 1] = __fadd_rn(__fmul_rn(y[i], sv), __fmul_rn(y[i + 1], c));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) o[i] = y[i];
+        }
+        *reinterpret_cast<uint4*>(out + dst) =
+            make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
+    };
+    if (p.q_out) finish(xq, sq, p.wq, p.q_out);
+    if (p.k_out) finish(xk, sk, p.wk, p.k_out);
+}
+
+}  // namespace fvprep
+
+extern "C" int fv_wan_qk_prep_bf16(void* stream, const void* proj, int width, int col_q, int col_k, int col_v,
+                                   const float* wq, const float* wk, const float* cosv, const float* sinv, int batch,
+                                   int seq, int heads, int d, float eps, int norm_scope, void* q_out, void* k_out,
+                                   void* v_out) {
+    fvrt::clear_error();
+    if (d != 128 || batch <= 0 || seq <= 0 || heads <= 0 || heads > 64) return FV_DECLINED;
+    if ((long long)batch * seq > 0x7fffffffll) return FV_DECLINED;
+    int dev;
+    int rc = fvrt::require_sm100(&dev);
+    if (rc != FV_RAN) return rc;
+    if (!proj || (!q_out && !k_out && !v_out)) return fvrt::fail(FV_ERR_INVALID, "qk_prep: null operand");
+    if ((q_out && !wq) || (k_out && !wk)) return fvrt::fail(FV_ERR_INVALID, "qk_prep: missing norm weight");
+    if ((cosv == nullptr) != (sinv == nullptr)) return fvrt::fail(FV_ERR_INVALID, "qk_prep: cos and sin go together");
+    if (norm_scope != FV_NORM_ACROSS_HEADS && norm_scope != FV_NORM_PER_HEAD)
+        return fvrt::fail(FV_ERR_INVALID, "qk_prep: unknown norm scope %d", norm_scope);
+    const int dim = heads * d;
+    auto bad_col = [&](int c) { return c < 0 || (c & 7) || c + dim > width; };
+    if ((width & 7) || (q_out && bad_col(col_q)) || (k_out && bad_col(col_k)) || (v_out && bad_col(col_v)))
+        return fvrt::fail(FV_ERR_INVALID, "qk_prep: columns must be multiples of 8 inside the row (width %d)", width);
+    const uintptr_t al = (uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_out | (uintptr_t)v_out | (uintptr_t)wq |
+                         (uintptr_t)wk | (uintptr_t)cosv | (uintptr_t)sinv;
+    if (al & 15) return fvrt::fail(FV_ERR_INVALID, "qk_prep: pointers must be 16-byte aligned");
+    fvprep::Params p{};
+    p.proj = (const __nv_bfloat16*)proj;
+    p.wq = wq;
+    p.wk = wk;
+    p.cosv = cosv;
+    p.sinv = sinv;
+    p.q_out = (__nv_bfloat16*)q_out;
+    p.k_out = (__nv_bfloat16*)k_out;
+    p.v_out = (__nv_bfloat16*)v_out;
+    p.batch = batch;
+    p.seq = seq;
+    p.heads = heads;
+    p.width = width;
+    p.col_q = col_q;
+    p.col_k = col_k;
+    p.col_v = col_v;
+    p.eps = eps;
+    p.per_head = norm_scope == FV_NORM_PER_HEAD;
+    const int threads = heads * 16;
+    const size_t smem = 2 * (threads / 32 + 1) * sizeof(float);
+    fvprep::fv_wan_qk_prep_kernel<<<(unsigned)(batch * seq), threads, smem, (cudaStream_t)stream>>>(p);
+    FV_CUDA(cudaGetLastError());
+    return FV_RAN;
+}

@@ -175,6 +175,8 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
     }
 
     if (warp < 8) {
+        // Register budget: the CTA's pool is what the launch allocated, 384 x 168 = 64512.
+        // 256 x 224 + 128 x 56 = 64512 exactly; asking for more blocks the warpgroup forever.
         asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
         // ------------------------------------------------------------ softmax
         WaitCtl ctl{abort_ptr, p.status, 3};
@@ -346,7 +348,7 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
         return;
     }
 
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
     if (warp == 8) {
         // ------------------------------------------------------- TMA producer
         if (lane == 0) {

@@ -90,6 +90,142 @@ FV_API int fv_sdpa_segments_bf16(void* stream, const void* q, const void* k, con
                           float scale, int mask_mode, int block_tokens, int window, int sink, int q_row0,
                           float* lse_out, const float* prev_o, const float* prev_lse);
 
+/* ---- Wan q/k prologue -------------------------------------------------------------
+ * Replaces the two CudaTensor::qk_norm_rope_bhsd launches and the split_heads_bhsd launch of
+ * WanAttention::forward_self (crates/fastvideo-cudarc/src/wan/transformer.rs:163-178,287-289;
+ * rt/fused.rs:193-330; host twin rt/ops.rs:2304-2371) by one pass.
+ *
+ * proj [batch, seq, width] bf16: the (fused) projection; q, k and v occupy columns
+ *   [col_x, col_x + heads*128) of each row.  wq, wk f32 [heads*128]: RMSNorm weights.
+ * cosv, sinv f32 [seq, 128] (both or neither; null = no rotation): the 3-D RoPE tables
+ *   of fv_wan_rope_tables.  eps: RMSNorm epsilon (1e-6 for Wan).
+ * norm_scope FV_NORM_ACROSS_HEADS: mean(x^2) over all heads*128 values of the row (Wan);
+ *   FV_NORM_PER_HEAD: over one head's 128 values.
+ * q_out, k_out, v_out [batch*heads, seq, 128] bf16; any may be null to skip it.
+ * Declines: d != 128, heads > 64, empty sizes. */
+FV_API int fv_wan_qk_prep_bf16(void* stream, const void* proj, int width, int col_q, int col_k, int col_v,
+                               const float* wq, const float* wk, const float* cosv, const float* sinv, int batch,
+                               int seq, int heads, int d, float eps, int norm_scope, void* q_out, void* k_out,
+                               void* v_out);
+
+/* ---- the kernel-selection plugin ------------------------------------------------------
+ * rt::sdpa_rule (crates/fastvideo-cudarc/src/rt/sdpa_rule.rs) as C: the Probe trait
+ * (:321-350) becomes plain data, the enums keep their order, and one kernel is added:
+ * FV_KERNEL_B200, this library's sm_100a kernel (seam value "b200"; the `auto` pick where
+ * b200_loaded is set).  All functions are pure and run without a GPU. */
+#define FV_BACKEND_DENSE 0
+#define FV_BACKEND_CUBLAS 1
+#define FV_BACKEND_FLASH 2
+#define FV_BACKEND_HOST 3
+#define FV_BACKEND_SPARSE 4
+
+#define FV_KERNEL_V1 0
+#define FV_KERNEL_V2 1
+#define FV_KERNEL_V3 2
+#define FV_KERNEL_V3S 3
+#define FV_KERNEL_CUDNN 4
+#define FV_KERNEL_DC 5
+#define FV_KERNEL_B200 6
+
+#define FV_STEP_RETIRED 0
+#define FV_STEP_FLASH_F32 1
+#define FV_STEP_SAGE 2
+#define FV_STEP_MMA 3
+#define FV_STEP_CUBLAS 4
+#define FV_STEP_COMPOSED 5
+
+#define FV_MMA_FIXED 0
+#define FV_MMA_RULE 1
+#define FV_MMA_TIMED 2
+
+typedef struct fv_probe {
+    int backend;            /* FASTVIDEO_SDPA, FV_BACKEND_* */
+    int sp_world;           /* FASTVIDEO_SP_WORLD, >= 1 */
+    int mma_default;        /* a bf16 tensor-core device is expected */
+    int has_sage;           /* SageAttention2 on */
+    int sage_min_seq;
+    int fp8_dense;
+    int causal_flash;       /* FASTVIDEO_WAN_CAUSAL_FLASH */
+    char kernel_choice[32]; /* FASTVIDEO_FLASH_KERNEL / [kernels] dense_attention, lower case */
+    int has_sm;             /* a device is present */
+    int sm_major;
+    int sms;
+    int dc_loaded;          /* the reference's attn_dc module is loaded */
+    int b200_loaded;        /* this library is loaded on a compute-capability 10.x device */
+    int auto_timed;         /* FASTVIDEO_SDPA_AUTO=timed */
+    int cudnn_has_plan;
+} fv_probe;
+
+typedef struct fv_step {
+    int kind;     /* FV_STEP_* */
+    int out_bf16; /* Sage, Mma */
+    int retired;  /* Retired: the FV_BACKEND_* that was asked for */
+} fv_step;
+
+/* The settings and the current device as a probe (reads the FASTVIDEO_* variables each call;
+ * without a device has_sm = 0, mma_default = 0, b200_loaded = 0).  Never fails. */
+FV_API void fv_probe_live(fv_probe* out);
+/* Defaults of a B200 with this library loaded and no variable set. */
+FV_API void fv_probe_default(fv_probe* out);
+
+FV_API int fv_rule_parse_backend(const char* v);
+FV_API int fv_rule_parse_auto_timed(const char* v);
+/* -1 when v is not a fixed kernel of the H3-VAE override (auto, dc, b200, anything else) */
+FV_API int fv_rule_parse_kernel_override(const char* v);
+FV_API int fv_rule_flash_v2_fills(size_t sq, size_t bh, size_t sms);
+/* 0 = cuDNN, 1 = flash_mma_fwd2 */
+FV_API int fv_rule_pick(int sm_major, size_t sq, size_t sk, size_t d);
+/* dims_ok[0] is set when k == [b, h, sk, d] of q and v == k (Shape::of) */
+FV_API void fv_rule_shape_of(const size_t q[4], const size_t k[4], const size_t v[4], size_t* sq, size_t* sk,
+                             int* dims_ok);
+/* Writes the route (at most 5 steps) and returns its length. */
+FV_API int fv_rule_dense_route(const size_t q[4], const size_t k[4], const size_t v[4], int masked, int out_bf16,
+                               const fv_probe* p, fv_step steps[8]);
+FV_API int fv_rule_flash_kernel_for(size_t sq, size_t bh, size_t sms, const fv_probe* p);
+/* Returns FV_MMA_*; *kernel gets the FV_KERNEL_* of Fixed and Rule, *sm_major that of Rule. */
+FV_API int fv_rule_mma_kernel(const size_t q[4], const size_t k[4], const size_t v[4], int out_bf16,
+                              const fv_probe* p, int* kernel, int* sm_major);
+FV_API int fv_rule_fp8_first(const fv_probe* p);
+FV_API int fv_rule_block_causal_first(const fv_probe* p);
+FV_API int fv_rule_vdn_window_first(const fv_probe* p);
+FV_API int fv_rule_kv_window_flash(int flash /* -1 unset */, const fv_probe* p);
+FV_API int fv_rule_mma_sdpa_supported(size_t b, size_t h, size_t sq, size_t sk, size_t d, int sm_major);
+
+/* ---- the one attention entry ----------------------------------------------------------
+ * rt::sdpa::sdpa(q, k, v, &Plan) (crates/fastvideo-cudarc/src/rt/sdpa.rs:27-164) for bf16
+ * BHSD operands on the device.  The plan says what the call computes; which kernel runs is
+ * fv_rule_*'s choice from `probe` (null = fv_probe_live).  FV_RAN: this library's kernel ran
+ * and `out` ([b, h, sq, d], bf16 when out_is_bf16 else f32) is being written on `stream`.
+ * FV_DECLINED: the chosen step is not this library's (cuBLAS, composed, another kernel, an
+ * additive mask, a head dim other than 128 ...): nothing was launched and the caller runs that
+ * step itself.  Errors: rank / shape mismatch ("sdpa expects BHSD"), a retired backend. */
+#define FV_PLAN_DENSE 0        /* Plan::dense / Plan::masked (mask may be set) */
+#define FV_PLAN_COMPOSED 1     /* Plan::composed: never ours */
+#define FV_PLAN_BLOCK_CAUSAL 2 /* Plan::block_causal */
+#define FV_PLAN_VDN_WINDOW 3   /* Plan::vdn_window: never ours */
+#define FV_PLAN_KV_WINDOW 4    /* Plan::kv_window / kv_window_with */
+
+typedef struct fv_plan {
+    int kind;
+    int has_scale;    /* 0: scale = 1/sqrt(d) */
+    float scale;
+    int has_mask;     /* Dense / Composed: an additive [.., sq, sk] mask is present */
+    int fp8_first;
+    int block_tokens; /* BlockCausal */
+    int window;
+    int sink;
+    int kv_flash;     /* KvWindow: -1 unset, 0, 1 */
+} fv_plan;
+
+FV_API int fv_sdpa(void* stream, const void* q, const void* k, const void* v, const size_t q_shape[4],
+                   const size_t k_shape[4], const size_t v_shape[4], const fv_plan* plan, const fv_probe* probe,
+                   void* out, int out_is_bf16);
+
+/* ---- sequence-parallel split ------------------------------------------------------------
+ * sp::shard_ranges (crates/fastvideo-cudarc/src/rt/sp.rs:16-28): contiguous shards, the
+ * remainder going to the low ranks.  start and len are host arrays of `world` ints. */
+FV_API void fv_shard_ranges(int seq, int world, int* start, int* len);
+
 #ifdef __cplusplus
 }
 #endif
