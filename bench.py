@@ -1,0 +1,337 @@
+#!/usr/bin/env python
+"""Benchmark of the Wan self-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One "step" = one pass of the path over one synthetic batch: the fused QKV projection (bf16, seeded
+N(0,1)) goes through the q/k prologue kernel (RMSNorm across heads + 3-D RoPE + head split) and the
+attention kernel.  Default workload: Wan2.1-14B 720p x 81 frames dense self-attention (1 x 40 heads x
+75 600 tokens x 128), sequence-parallel over N GPUs (token shards; one NCCL all-gather of K and V per
+step, overlapped with attention over the local keys).  Total work is fixed as N grows ("strong").
+
+Prints ONE JSON line (rank 0).  FLOPs = 4 * bh * sq * sk_visible * d (the reference's formula,
+crates/fastvideo-gpucheck/src/kernels/attn2.rs:466).  `value` is whole-job TFLOP/s with inputs resident
+in HBM; `e2e` is the same metric with the projection coming from pinned host memory and the result
+going back to the host inside the timed region.
+
+--impl reference times the reference's CPU path (its composed f32 SDPA after the host q/k norm + RoPE,
+restated in oracle/fv_oracle.cpp because the reference is Rust and no Rust toolchain exists here) on all
+host threads, on a bounded sample of query rows of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: batch, heads, grid (frames, h, w in patches), causal block tokens (0 = dense), cross keys
+    "wan14b_720p_dense": dict(batch=1, heads=40, grid=(21, 45, 80), block=0, desc="Wan2.1-14B 720p x81f dense self-attention"),
+    "wan1p3b_480p_dense": dict(batch=2, heads=12, grid=(21, 30, 52), block=0, desc="Wan2.1-1.3B 480p x81f dense self-attention, CFG pair"),
+    "wan1p3b_480p_causal": dict(batch=1, heads=12, grid=(21, 30, 52), block=4680, desc="Self-Forcing chunk-causal (7 chunks x 3 frames) at the Wan-1.3B shape"),
+    "tiny": dict(batch=1, heads=12, grid=(3, 8, 8), block=0, desc="tiny Wan-arch dense self-attention (192 tokens)"),
+}
+METRIC = "Wan self-attn TFLOP/s (dense, prologue + attention), whole job"
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(burst=float(d["bf16_tflops"]), sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    hbm=float(d["hbm_gbs"]), source="measured")
+    return dict(burst=1590.0, sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+def visible_pairs(seq: int, block: int) -> float:
+    """Query-key pairs the mask lets through (dense: seq^2)."""
+    if block <= 0:
+        return float(seq) * seq
+    total = 0.0
+    for c0 in range(0, seq, block):
+        rows = min(block, seq - c0)
+        total += rows * float(min(seq, c0 + block))
+    return total
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs (read-only)."""
+    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); pw.append(float(f[3]))
+            except ValueError:
+                continue
+            for n, val in zip(names, f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        sm.sort()
+        return dict(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx), power_w_max=max(pw), samples=len(sm), reasons=sorted(reasons))
+
+
+def reference_arm(args, wl):
+    """The reference's CPU path on the host cores, on a bounded sample of the workload.
+
+    Attention: `cpu_rows` query rows x `cpu_heads` heads against ALL keys of those heads (the composed f32
+    SDPA).  Prologue: the host q/k RMSNorm + RoPE + head split on `cpu_tokens` tokens, all heads.  Both
+    are scaled to the full workload by the work they cover (rows x heads, tokens) and combined into the
+    same whole-step TFLOP/s the GPU arm reports."""
+    import numpy as np
+    from oracle import oracle as O
+    O.build()
+    batch, heads, grid, block = wl["batch"], wl["heads"], wl["grid"], wl["block"]
+    seq = grid[0] * grid[1] * grid[2]
+    dim = heads * 128
+    hs = min(args.cpu_heads, heads)
+    rows = np.sort(np.random.default_rng(0).choice(seq, size=min(args.cpu_rows, seq), replace=False)).astype(np.int32)
+    q, k, v = (O.bf16_round(O.seeded_normal(args.seed, 10 + i, (hs, seq, 128))) for i in range(3))
+    causal = (block, 0, 0) if block else None
+    ntok = min(args.cpu_tokens, seq)
+    proj = O.bf16_round(O.seeded_normal(args.seed, 0, (1, ntok, 3 * dim)))
+    w = np.ones(dim, np.float32)
+    cos, sin = O.wan_rope(*grid)
+    cos, sin = cos[:ntok].copy(), sin[:ntok].copy()
+    t_attn, t_prep = [], []
+    for i in range(args.warmup_cpu + args.steps_cpu):
+        t0 = time.perf_counter()
+        O.sdpa_rows(q, k, v, rows=rows, block_causal=causal)
+        t1 = time.perf_counter()
+        O.qk_norm_rope_bhsd(proj, w, cos, sin, 1, ntok, heads, 128, 3 * dim, 0)
+        O.qk_norm_rope_bhsd(proj, w, cos, sin, 1, ntok, heads, 128, 3 * dim, dim)
+        O.split_heads_bhsd(proj, 1, ntok, heads, 128, 3 * dim, 2 * dim)
+        t2 = time.perf_counter()
+        if i >= args.warmup_cpu:
+            t_attn.append(t1 - t0)
+            t_prep.append(t2 - t1)
+    ta, tp = sorted(t_attn)[len(t_attn) // 2], sorted(t_prep)[len(t_prep) // 2]
+    if block:
+        vis_rows = sum(min(seq, (int(r) // block + 1) * block) for r in rows)
+    else:
+        vis_rows = len(rows) * seq
+    sample_flops = 4.0 * hs * vis_rows * 128
+    total_flops = 4.0 * batch * heads * visible_pairs(seq, block) * 128
+    full_seconds = ta * (total_flops / sample_flops) + tp * (batch * seq / ntok)
+    return dict(value=total_flops / full_seconds / 1e12, seconds=ta + tp, cores=O.num_threads(), attn_tflops=sample_flops / ta / 1e12,
+                sample=f"attention: {len(rows)} of {seq} query rows x {hs} of {heads} heads x all keys ({sample_flops / 1e9:.1f} GFLOP in "
+                       f"{ta:.2f} s); prologue: {ntok} of {batch * seq} tokens x all heads ({tp:.2f} s); scaled to the whole step by "
+                       f"rows x heads and tokens (extrapolated whole step: {full_seconds:.0f} s)")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="wan14b_720p_dense", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seed", type=int, default=20260927)
+    ap.add_argument("--cpu-rows", type=int, default=2048, help="query rows of the CPU-baseline sample")
+    ap.add_argument("--cpu-heads", type=int, default=4, help="heads of the CPU-baseline sample")
+    ap.add_argument("--cpu-tokens", type=int, default=4096, help="tokens of the CPU-baseline prologue sample")
+    ap.add_argument("--steps-cpu", type=int, default=1)
+    ap.add_argument("--warmup-cpu", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    batch, heads, grid, block = wl["batch"], wl["heads"], wl["grid"], wl["block"]
+    seq = grid[0] * grid[1] * grid[2]
+    dim = heads * 128
+    total_flops = 4.0 * batch * heads * visible_pairs(seq, block) * 128
+    cfg = dict(workload=f"{args.workload}: {wl['desc']}; b{batch} h{heads} S{seq} d128", seed=args.seed,
+               l2="inputs exceed L2 (no flush needed)" if batch * seq * dim * 2 * 3 > 2 * 126e6 else "L2 flushed between steps",
+               parallelism=f"sp{world}" if world > 1 else "single")
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        # whole --steps/--warmup run of bounded samples
+        args.steps_cpu, args.warmup_cpu = max(1, min(args.steps, 3)), min(args.warmup, 1)
+        r = reference_arm(args, wl)
+        line = dict(metric=METRIC, value=r["value"], unit="TFLOP/s", n_gpus=args.gpus, steps=args.steps_cpu, warmup=args.warmup_cpu,
+                    ms_per_step=r["seconds"] * 1e3, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32",
+                    data="synthetic", config=cfg, impl="reference",
+                    cpu_baseline=dict(value=r["value"], unit="TFLOP/s", cores=r["cores"], kind="port", sample=r["sample"]),
+                    e2e=dict(value=r["value"], unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+    from fastvideo_rs_b200 import sdpa, sp, wan
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: the kernels have no CPU path (use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if world != args.gpus and rank == 0:
+        print(f"note: --gpus {args.gpus} but WORLD_SIZE {world}; using {world}", file=sys.stderr)
+
+    # ---- synthetic inputs, resident in HBM: this rank's token shard of the fused QKV projection
+    start, length = sp.shard_ranges(seq, world)[rank]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(args.seed + rank)
+    proj = torch.randn((batch, length, 3 * dim), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    wq = torch.ones(dim, device=dev)
+    wk = torch.ones(dim, device=dev)
+    cos_all, sin_all = wan.wan_rope_tables_host(grid)
+    cos = torch.from_numpy(cos_all[start:start + length].copy()).to(dev)
+    sin = torch.from_numpy(sin_all[start:start + length].copy()).to(dev)
+    bh = batch * heads
+    causal = sdpa.BlockCausal(block, 0, 0) if block else None
+    if world > 1 and causal is not None:
+        raise SystemExit("the chunk-causal workload is single-GPU in this bench")
+    spa = sp.SpAttention(seq, bh, device=dev) if world > 1 else None
+    out_buf = torch.empty((bh, length, 128), dtype=torch.bfloat16, device=dev)
+    launches_per_step = 2 if world == 1 else 3
+    attn_events = []
+
+    def step(p, record=False):
+        q, k, v = wan.qk_prep(p, wq, wk, cos, sin, heads)
+        q, k, v = q.view(bh, length, 128), k.view(bh, length, 128), v.view(bh, length, 128)
+        if record:
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+        if spa is not None:
+            o = spa.forward(q, k, v, out=out_buf)
+        else:
+            o = sdpa.dense_fwd(q, k, v, causal=causal, out=out_buf)
+        if record:
+            e1.record()
+            attn_events.append((e0, e1))
+        return o
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step(proj)
+    barrier()
+    assert sdpa.device_status() == 0
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        step(proj, record=True)
+    t1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = t0.elapsed_time(t1)
+    attn_ms = sum(a.elapsed_time(b) for a, b in attn_events) / len(attn_events)
+    assert sdpa.device_status() == 0
+
+    # ---- end to end through the public API: pinned host projection in, host result out, every step
+    e2e = None
+    if not args.no_e2e:
+        host_in = torch.empty(proj.shape, dtype=torch.bfloat16, pin_memory=True)
+        host_in.copy_(proj)
+        host_out = torch.empty(out_buf.shape, dtype=torch.bfloat16, pin_memory=True)
+        dev_in = torch.empty_like(proj)
+        n_e2e = max(2, min(args.steps, 5))
+
+        def e2e_step():
+            dev_in.copy_(host_in, non_blocking=True)
+            o = step(dev_in)
+            host_out.copy_(o, non_blocking=True)
+
+        e2e_step()
+        barrier()
+        a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        b.record()
+        barrier()
+        e2e_ms = a.elapsed_time(b) / n_e2e
+    t = torch.tensor([ms_total, attn_ms, e2e_ms if not args.no_e2e else 0.0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, attn_ms, e2e_ms = (float(x) for x in t.tolist())
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    ms_step = ms_total / args.steps
+    value = total_flops / (ms_step * 1e-3) / 1e12
+    pk = peaks()
+    rank_flops = total_flops / world
+    achieved = rank_flops / (attn_ms * 1e-3) / 1e12
+    traffic = None
+    tf = ROOT / "profiles" / "traffic.json"
+    if tf.exists():
+        try:
+            traffic = json.loads(tf.read_text()).get(args.workload)
+        except Exception:
+            traffic = None
+    line = dict(metric=METRIC, value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+                ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
+                config=cfg, per_gpu_tflops=value / world, frac_of_bf16_peak_burst=value / world / pk["burst"],
+                frac_of_bf16_peak_sustained=value / world / pk["sustained"], peaks=pk,
+                roofline=dict(bound="tensor", kernel="fv_sdpa_fwd_d128", achieved=achieved, peak=pk["sustained"], unit="TFLOP/s",
+                              frac=achieved / pk["sustained"], frac_of_burst=achieved / pk["burst"], of=pk["source"],
+                              ms_per_launch_set=attn_ms, traffic=traffic,
+                              note="attention launch(es) of one step timed with CUDA events inside the timed region; "
+                                   "at N>1 this includes waiting for the K/V all-gather"),
+                clocks=clocks, gpu_launches=launches_per_step * args.steps)
+    if not args.no_e2e:
+        line["e2e"] = dict(value=total_flops / (e2e_ms * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=e2e_ms,
+                           h2d_bytes_per_step=proj.numel() * 2 * world, d2h_bytes_per_step=out_buf.numel() * 2 * world)
+    if world == 1 and not args.no_cpu_baseline:
+        r = reference_arm(args, wl)
+        line["cpu_baseline"] = dict(value=r["value"], unit="TFLOP/s", cores=r["cores"], kind="port", sample=r["sample"],
+                                    seconds=r["seconds"])
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -12,6 +12,9 @@
 // Only the order of the sum of squares differs (tree reduction instead of a sequential sum).
 #include "fv_runtime.h"
 #include <cuda_bf16.h>
+#include <math.h>
+#include <string.h>
+#include <vector>
 
 namespace fvprep {
 
@@ -178,5 +181,49 @@ extern "C" int fv_wan_qk_prep_bf16(void* stream, const void* proj, int width, in
     const size_t smem = 2 * (threads / 32 + 1) * sizeof(float);
     fvprep::fv_wan_qk_prep_kernel<<<(unsigned)(batch * seq), threads, smem, (cudaStream_t)stream>>>(p);
     FV_CUDA(cudaGetLastError());
+    return FV_RAN;
+}
+
+// 3-D RoPE tables of Wan on the host: wan_rope_at / rotary_1d,
+// crates/fastvideo-cudarc/src/wan/transformer.rs:447-463,490-544.  freq = 1/theta^(2i/dim) in f64
+// narrowed to f32, angle = position (f32) * freq in f32, cosf / sinf, each value twice
+// (interleaved pairs); row = [t | h | w] with h = w = 2*(d/6), t = d - h - w.
+extern "C" int fv_wan_rope_tables(int ppf, int pph, int ppw, int d, double theta, int start_frame, float* cos_host,
+                                  float* sin_host) {
+    fvrt::clear_error();
+    if (ppf <= 0 || pph <= 0 || ppw <= 0 || d <= 0 || (d & 1) || start_frame < 0 || !cos_host || !sin_host)
+        return fvrt::fail(FV_ERR_INVALID, "rope tables: bad grid (%d, %d, %d) or head dim %d", ppf, pph, ppw, d);
+    const int h_dim = 2 * (d / 6), w_dim = h_dim, t_dim = d - h_dim - w_dim;
+    auto axis = [&](int dim, int n, std::vector<float>& c, std::vector<float>& s) {
+        c.assign((size_t)n * dim, 0.f);
+        s.assign((size_t)n * dim, 0.f);
+        for (int i = 0; i < dim / 2; i++) {
+            const float freq = (float)(1.0 / pow(theta, 2.0 * (double)i / (double)dim));
+            for (int pos = 0; pos < n; pos++) {
+                const float arg = (float)pos * freq;
+                const float cv = cosf(arg), sv = sinf(arg);
+                c[(size_t)pos * dim + 2 * i] = c[(size_t)pos * dim + 2 * i + 1] = cv;
+                s[(size_t)pos * dim + 2 * i] = s[(size_t)pos * dim + 2 * i + 1] = sv;
+            }
+        }
+    };
+    std::vector<float> ct, st, ch, sh, cw, sw;
+    axis(t_dim, start_frame + ppf, ct, st);
+    axis(h_dim, pph, ch, sh);
+    axis(w_dim, ppw, cw, sw);
+    size_t o = 0;
+    for (int ft = start_frame; ft < start_frame + ppf; ft++)
+        for (int fh = 0; fh < pph; fh++)
+            for (int fw = 0; fw < ppw; fw++) {
+                memcpy(cos_host + o, &ct[(size_t)ft * t_dim], sizeof(float) * t_dim);
+                memcpy(sin_host + o, &st[(size_t)ft * t_dim], sizeof(float) * t_dim);
+                o += t_dim;
+                memcpy(cos_host + o, &ch[(size_t)fh * h_dim], sizeof(float) * h_dim);
+                memcpy(sin_host + o, &sh[(size_t)fh * h_dim], sizeof(float) * h_dim);
+                o += h_dim;
+                memcpy(cos_host + o, &cw[(size_t)fw * w_dim], sizeof(float) * w_dim);
+                memcpy(sin_host + o, &sw[(size_t)fw * w_dim], sizeof(float) * w_dim);
+                o += w_dim;
+            }
     return FV_RAN;
 }

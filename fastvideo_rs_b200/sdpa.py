@@ -1,0 +1,150 @@
+"""The one attention entry: rt::sdpa::sdpa(q, k, v, &Plan) (crates/fastvideo-cudarc/src/rt/sdpa.rs:27-164)
+over torch CUDA tensors.  The Plan constructors keep the reference's names.  Which kernel runs is
+sdpa_rule's choice; when that choice is not this library's sm_100a kernel the call raises
+``Declined`` -- this package has no other kernel and no CPU path."""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+from . import sdpa_rule
+
+
+@dataclass(frozen=True)
+class BlockCausal:
+    """Wan's block-causal temporal mask as kernel parameters (rt/attn.rs:434-453): query q sees key k
+    iff (block(k) <= block(q) and (window == 0 or block(q) - block(k) < window)) or block(k) < sink."""
+    block_tokens: int
+    window: int = 0
+    sink: int = 0
+
+    def allows(self, q: int, k: int) -> bool:
+        bt = max(self.block_tokens, 1)
+        tq, tk = q // bt, k // bt
+        return (tk <= tq and (self.window == 0 or tq - tk < self.window)) or tk < self.sink
+
+
+_DENSE, _COMPOSED, _BLOCK_CAUSAL, _VDN_WINDOW, _KV_WINDOW = range(5)
+
+
+@dataclass(frozen=True)
+class Plan:
+    """What one attention call computes (rt/sdpa.rs:27-139)."""
+    kind: int = _DENSE
+    scale: Optional[float] = None
+    mask: Optional[torch.Tensor] = None
+    fp8_first_: bool = False
+    causal: Optional[BlockCausal] = None
+    flash: Optional[bool] = None
+
+    @staticmethod
+    def dense(scale: Optional[float] = None) -> "Plan":
+        return Plan(_DENSE, scale)
+
+    @staticmethod
+    def masked(scale: Optional[float], mask: Optional[torch.Tensor]) -> "Plan":
+        return Plan(_DENSE, scale, mask)
+
+    def fp8_first(self) -> "Plan":
+        if self.kind == _DENSE and self.mask is None:
+            return Plan(_DENSE, self.scale, None, True)
+        return self
+
+    @staticmethod
+    def composed(scale: Optional[float], mask: Optional[torch.Tensor]) -> "Plan":
+        return Plan(_COMPOSED, scale, mask)
+
+    @staticmethod
+    def block_causal(scale: Optional[float], mask: BlockCausal) -> "Plan":
+        return Plan(_BLOCK_CAUSAL, scale, causal=mask)
+
+    @staticmethod
+    def kv_window() -> "Plan":
+        return Plan(_KV_WINDOW)
+
+    @staticmethod
+    def kv_window_with(flash: bool) -> "Plan":
+        return Plan(_KV_WINDOW, flash=flash)
+
+    def to_c(self) -> _lib.PlanC:
+        c = _lib.PlanC()
+        c.kind = self.kind
+        c.has_scale = int(self.scale is not None)
+        c.scale = float(self.scale or 0.0)
+        c.has_mask = int(self.mask is not None)
+        c.fp8_first = int(self.fp8_first_)
+        if self.causal is not None:
+            c.block_tokens, c.window, c.sink = self.causal.block_tokens, self.causal.window, self.causal.sink
+        c.kv_flash = -1 if self.flash is None else int(self.flash)
+        return c
+
+
+def _stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check_bf16_cuda(name: str, t: torch.Tensor) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor: this package has no CPU path")
+    if t.dtype != torch.bfloat16:
+        raise ValueError(f"{name} must be bfloat16 (the reference rounds operands to bf16 under bf16 activations)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous BHSD")
+
+
+def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, plan: Plan, *, out_bf16: bool = True,
+         probe: Optional[sdpa_rule.Probe] = None) -> torch.Tensor:
+    """Scaled dot-product attention over BHSD q [b, h, sq, d], k / v [b, h, sk, d], as `plan` says.
+    Returns [b, h, sq, d] (bf16, or f32 with out_bf16=False).  Asynchronous on the current stream."""
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("sdpa expects BHSD")
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _check_bf16_cuda(n, t)
+    out = torch.empty(q.shape, dtype=torch.bfloat16 if out_bf16 else torch.float32, device=q.device)
+    cs4 = ctypes.c_size_t * 4
+    pc = plan.to_c()
+    pr = probe.to_c() if probe is not None else None
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().fv_sdpa(_stream_ptr(), ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()),
+                                ctypes.c_void_p(v.data_ptr()), cs4(*q.shape), cs4(*k.shape), cs4(*v.shape),
+                                ctypes.byref(pc), ctypes.byref(pr) if pr is not None else None,
+                                ctypes.c_void_p(out.data_ptr()), int(out_bf16))
+    _lib.check(rc, "sdpa")
+    return out
+
+
+def dense_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: Optional[float] = None,
+              out_bf16: bool = True, causal: Optional[BlockCausal] = None, q_row0: int = 0,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The kernel-level call (attn_dc::dense_fwd, rt/attn_dc.rs:213-273): q [bh, sq, 128],
+    k / v [bh, sk, 128] bf16 -> [bh, sq, 128]."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _check_bf16_cuda(n, t)
+    bh, sq, d = q.shape
+    sk = k.shape[1]
+    if k.shape != (bh, sk, d) or v.shape != k.shape:
+        raise ValueError("dense_fwd: k and v must be [bh, sk, d] of q")
+    scale = float(scale) if scale is not None else 1.0 / d ** 0.5
+    if out is None:
+        out = torch.empty((bh, sq, d), dtype=torch.bfloat16 if out_bf16 else torch.float32, device=q.device)
+    mode, bt, win, sink = (1, causal.block_tokens, causal.window, causal.sink) if causal else (0, 0, 0, 0)
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().fv_sdpa_dense_bf16(_stream_ptr(), ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()),
+                                           ctypes.c_void_p(v.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+                                           int(out.dtype == torch.bfloat16), bh, sq, sk, d, ctypes.c_float(scale),
+                                           mode, bt, win, sink, q_row0)
+    _lib.check(rc, "dense_fwd")
+    return out
+
+
+def device_status() -> int:
+    """Synchronises the current stream and returns the kernels' status word (0 = every bounded wait
+    completed); raises FvError when a kernel gave up."""
+    code = ctypes.c_int(0)
+    rc = _lib.lib().fv_device_status(_stream_ptr(), ctypes.byref(code))
+    _lib.check(rc, "device_status")
+    return code.value

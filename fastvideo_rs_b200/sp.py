@@ -1,0 +1,125 @@
+"""Sequence parallelism for the attention call: one process per GPU, contiguous token shards
+(sp::shard_ranges, crates/fastvideo-cudarc/src/rt/sp.rs:16-28), ONE exchange -- an NCCL all-gather
+of the rank's bf16 K and V shards into every rank's own HBM -- overlapped with attention over the
+local keys; the output stays sharded.  (The reference replicates K/V on every rank and gathers the
+outputs through the host, rt/sdpa.rs:354-410; this replaces that.)
+
+Pass 1 (compute stream): softmax(Q_r K_r^T) V_r, f32, with its log-sum-exp.
+Exchange (communication stream, concurrently): all-gather K, all-gather V.
+Pass 2 (compute stream, after the exchange): the same kernel over the other ranks' segments,
+merging pass 1 in its epilogue -- exactly the softmax over all keys."""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Tuple
+
+import torch
+
+from . import _lib
+from .sdpa import BlockCausal, _stream_ptr
+
+
+def shard_ranges(seq: int, world: int) -> List[Tuple[int, int]]:
+    """[(start, len)] per rank: contiguous, remainder to the low ranks."""
+    world = max(world, 1)
+    st = (ctypes.c_int * world)()
+    ln = (ctypes.c_int * world)()
+    _lib.lib().fv_shard_ranges(seq, world, st, ln)
+    return [(st[i], ln[i]) for i in range(world)]
+
+
+def shard_tensor(x: torch.Tensor, dim: int, rank: int, world: int) -> torch.Tensor:
+    """This rank's slice of `x` along `dim` (sp::shard_tensor, rt/sp.rs:41-49)."""
+    ranges = shard_ranges(x.shape[dim], world)
+    if not 0 <= rank < len(ranges):
+        raise ValueError(f"SP rank {rank} out of world {world}")
+    start, length = ranges[rank]
+    return x.narrow(dim, start, length)
+
+
+def all_gather_seq(shards: List[torch.Tensor], dim: int) -> torch.Tensor:
+    """Concatenate sequence shards (sp::all_gather_seq, rt/sp.rs:31-37)."""
+    if not shards:
+        raise ValueError("all_gather empty")
+    return torch.cat(shards, dim)
+
+
+def _i32(vals):
+    return (ctypes.c_int * len(vals))(*[int(v) for v in vals])
+
+
+def segments_fwd(q, k_all, v_all, seg_len, seg_start, seg_rows, scale, *, out=None, out_bf16=True, causal=None,
+                 q_row0=0, lse_out=None, prev_o=None, prev_lse=None):
+    """fv_sdpa_segments_bf16: q [bh, sq, 128]; k_all / v_all [nseg, bh, seg_rows, 128]."""
+    bh, sq, d = q.shape
+    nseg = len(seg_len)
+    if out is None:
+        out = torch.empty((bh, sq, d), dtype=torch.bfloat16 if out_bf16 else torch.float32, device=q.device)
+    mode, bt, win, sink = (1, causal.block_tokens, causal.window, causal.sink) if causal else (0, 0, 0, 0)
+    vp = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+    fp = lambda t: ctypes.cast(ctypes.c_void_p(t.data_ptr()), ctypes.POINTER(ctypes.c_float)) if t is not None else None
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().fv_sdpa_segments_bf16(_stream_ptr(), vp(q), vp(k_all), vp(v_all), vp(out),
+                                              int(out.dtype == torch.bfloat16), bh, sq, nseg, _i32(seg_len),
+                                              _i32(seg_start), seg_rows, ctypes.c_float(scale), mode, bt, win, sink,
+                                              q_row0, fp(lse_out), fp(prev_o), fp(prev_lse))
+    _lib.check(rc, "segments_fwd")
+    return out
+
+
+class SpAttention:
+    """Sequence-parallel dense attention for one (seq, bh) shape; buffers allocated once."""
+
+    def __init__(self, seq: int, bh: int, group=None, device=None):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.seq, self.bh = seq, bh
+        self.ranges = shard_ranges(seq, self.world)
+        self.start, self.len = self.ranges[self.rank]
+        self.seg_rows = max(l for _, l in self.ranges)
+        d = 128
+        if self.world > 1:
+            self.k_all = torch.zeros((self.world, bh, self.seg_rows, d), dtype=torch.bfloat16, device=self.device)
+            self.v_all = torch.zeros_like(self.k_all)
+            self.o1 = torch.empty((bh, self.len, d), dtype=torch.float32, device=self.device)
+            self.lse1 = torch.empty((bh, self.len), dtype=torch.float32, device=self.device)
+            self.comm_stream = torch.cuda.Stream(device=self.device)
+            self.pad = None
+            if self.len != self.seg_rows:
+                self.pad = (torch.zeros((bh, self.seg_rows, d), dtype=torch.bfloat16, device=self.device),
+                            torch.zeros((bh, self.seg_rows, d), dtype=torch.bfloat16, device=self.device))
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """q, k, v: this rank's [bh, len_r, 128] bf16 shards.  Returns this rank's [bh, len_r, 128] bf16."""
+        d = q.shape[-1]
+        scale = float(scale) if scale is not None else 1.0 / d ** 0.5
+        if self.world == 1:
+            return segments_fwd(q, k, v, [self.len], [0], self.len, scale, out=out)
+        cur = torch.cuda.current_stream(self.device)
+        if self.pad is not None:
+            self.pad[0][:, : self.len].copy_(k)
+            self.pad[1][:, : self.len].copy_(v)
+            ks, vs = self.pad
+        else:
+            ks, vs = k, v
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ready)
+            self.dist.all_gather_into_tensor(self.k_all, ks, group=self.group)
+            self.dist.all_gather_into_tensor(self.v_all, vs, group=self.group)
+            gathered = torch.cuda.Event()
+            gathered.record(self.comm_stream)
+        # pass 1: the local keys, while the exchange is in flight
+        segments_fwd(q, ks, vs, [self.len], [self.start], self.seg_rows, scale, out=self.o1, lse_out=self.lse1)
+        cur.wait_event(gathered)
+        # pass 2: every other rank's keys, merged with pass 1
+        lens = [l if r != self.rank else 0 for r, (_, l) in enumerate(self.ranges)]
+        starts = [s for s, _ in self.ranges]
+        return segments_fwd(q, self.k_all, self.v_all, lens, starts, self.seg_rows, scale, out=out,
+                            prev_o=self.o1, prev_lse=self.lse1)

@@ -108,6 +108,13 @@ FV_API int fv_wan_qk_prep_bf16(void* stream, const void* proj, int width, int co
                                int seq, int heads, int d, float eps, int norm_scope, void* q_out, void* k_out,
                                void* v_out);
 
+/* 3-D RoPE tables on the host: wan_rope_at (crates/fastvideo-cudarc/src/wan/transformer.rs:447-544).
+ * (ppf, pph, ppw): the token grid in patches; rows are tokens frame-major then height then width,
+ * each row [t | h | w] with h = w = 2*(d/6) and t = d - h - w (44/42/42 at d = 128).
+ * cos_host, sin_host: host arrays [ppf*pph*ppw, d] f32.  No GPU needed. */
+FV_API int fv_wan_rope_tables(int ppf, int pph, int ppw, int d, double theta, int start_frame, float* cos_host,
+                              float* sin_host);
+
 /* ---- the kernel-selection plugin ------------------------------------------------------
  * rt::sdpa_rule (crates/fastvideo-cudarc/src/rt/sdpa_rule.rs) as C: the Probe trait
  * (:321-350) becomes plain data, the enums keep their order, and one kernel is added:

@@ -1,0 +1,61 @@
+"""The q/k prologue kernel against the oracle's qk_norm_rope_bhsd / split_heads_bhsd."""
+import numpy as np
+import pytest
+import torch
+
+from _util import to_dev_bf16, to_host_f32
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("batch,grid,heads,per_head", [(1, (3, 8, 8), 12, False), (2, (2, 5, 7), 12, False),
+                                                       (1, (2, 4, 6), 40, False), (1, (2, 3, 5), 12, True),
+                                                       (1, (1, 1, 1), 1, False)])
+def test_prep_matches_oracle(fvlib, oracle, batch, grid, heads, per_head):
+    from fastvideo_rs_b200 import wan
+    seq = grid[0] * grid[1] * grid[2]
+    dim = heads * 128
+    proj = oracle.bf16_round(oracle.seeded_normal(31, 0, (batch, seq, 3 * dim)))
+    wq = (1.0 + 0.1 * oracle.seeded_normal(31, 1, (dim,))).astype(np.float32)
+    wk = (1.0 + 0.1 * oracle.seeded_normal(31, 2, (dim,))).astype(np.float32)
+    cos, sin = oracle.wan_rope(*grid)
+    tc, ts = wan.wan_rope_tables(grid)
+    assert np.array_equal(to_host_f32(tc), cos) and np.array_equal(to_host_f32(ts), sin)
+    q, k, v = wan.qk_prep(to_dev_bf16(proj), torch.from_numpy(wq).cuda(), torch.from_numpy(wk).cuda(), tc, ts, heads,
+                          norm_scope=wan.NORM_PER_HEAD if per_head else wan.NORM_ACROSS_HEADS)
+    want_q = oracle.qk_norm_rope_bhsd(proj, wq, cos, sin, batch, seq, heads, 128, 3 * dim, 0, 1e-6, per_head)
+    want_k = oracle.qk_norm_rope_bhsd(proj, wk, cos, sin, batch, seq, heads, 128, 3 * dim, dim, 1e-6, per_head)
+    want_v = oracle.split_heads_bhsd(proj, batch, seq, heads, 128, 3 * dim, 2 * dim)
+    gq = to_host_f32(q).reshape(batch * heads, seq, 128)
+    gk = to_host_f32(k).reshape(batch * heads, seq, 128)
+    gv = to_host_f32(v).reshape(batch * heads, seq, 128)
+    assert np.array_equal(gv, want_v)  # a copy: bit exact
+    # f32 arithmetic identical up to the order of the sum of squares, then ONE rounding to bf16: the
+    # result is the bf16 rounding of the oracle's value except where that value sits on a rounding tie
+    for got, want in ((gq, want_q), (gk, want_k)):
+        rounded = oracle.bf16_round(want)
+        mism = np.mean(got != rounded)
+        assert mism < 2e-3, f"{mism:.2e} of the elements differ from the rounded oracle"
+        assert np.abs(got - want).max() <= np.abs(want).max() * 2.0 ** -8
+
+
+def test_prep_without_rope_and_partial_outputs(fvlib, oracle):
+    from fastvideo_rs_b200 import wan
+    batch, seq, heads = 1, 50, 12
+    dim = heads * 128
+    proj = oracle.bf16_round(oracle.seeded_normal(32, 0, (batch, seq, dim)))
+    w = np.ones(dim, np.float32)
+    # cross-attention K: RMS-normed, no rotation, projection of width dim at column 0
+    _, k, _ = wan.qk_prep(to_dev_bf16(proj), None, torch.from_numpy(w).cuda(), None, None, heads, col_k=0,
+                          want_q=False, want_v=False)
+    want = oracle.qk_norm_rope_bhsd(proj, w, None, None, batch, seq, heads, 128, dim, 0, 1e-6)
+    got = to_host_f32(k).reshape(heads, seq, 128)
+    assert np.mean(got != oracle.bf16_round(want)) < 2e-3
+
+
+def test_prep_rejects_bad_columns(fvlib, oracle):
+    from fastvideo_rs_b200 import FvError, wan
+    proj = torch.zeros((1, 8, 1536), dtype=torch.bfloat16, device="cuda")
+    w = torch.ones(1536, device="cuda")
+    with pytest.raises(FvError):
+        wan.qk_prep(proj, w, w, None, None, 12)  # k and v columns fall outside a width-1536 row

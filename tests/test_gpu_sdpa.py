@@ -1,0 +1,205 @@
+"""Parity of the sm_100a attention kernel with the CPU oracle, through the C ABI (ctypes) on seeded
+inputs.  Tolerance: bf16 outputs within max-abs 2e-2 and mean-abs 2e-3 of the fp32 oracle."""
+import math
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from _util import assert_close, sample_rows, to_dev_bf16, to_host_f32
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def qkv(oracle, seed, bh, sq, sk):
+    q = oracle.bf16_round(oracle.seeded_normal(seed, 0, (bh, sq, 128)))
+    k = oracle.bf16_round(oracle.seeded_normal(seed, 1, (bh, sk, 128)))
+    v = oracle.bf16_round(oracle.seeded_normal(seed, 2, (bh, sk, 128)))
+    return q, k, v
+
+
+# the reference's parity shapes (scripts/gpu/upstream/attn_dc_bench.cu:466-471;
+# crates/fastvideo-gpucheck/src/kernels/attn2.rs:83-175) plus tile-edge lengths
+SHAPES = [(1, 1, 1), (2, 64, 64), (2, 128, 128), (1, 129, 127), (2, 256, 256), (3, 192, 192), (2, 63, 4097), (2, 130, 1),
+          (2, 300, 512), (2, 1000, 333), (4, 1024, 1024), (2, 257, 640), (2, 2048, 2048), (1, 65, 65)]
+
+
+@pytest.mark.parametrize("bh,sq,sk", SHAPES)
+def test_dense_matches_oracle(fvlib, oracle, bh, sq, sk):
+    from fastvideo_rs_b200 import sdpa
+    q, k, v = qkv(oracle, 100 + sq + sk, bh, sq, sk)
+    out = sdpa.dense_fwd(to_dev_bf16(q), to_dev_bf16(k), to_dev_bf16(v))
+    assert sdpa.device_status() == 0
+    want = oracle.sdpa_rows(q, k, v)
+    assert_close(to_host_f32(out), want, f"dense {bh}x{sq}x{sk}")
+
+
+def test_bf16_output_is_the_rounded_f32_output(fvlib, oracle):
+    """crates/fastvideo-gpucheck/src/kernels/attn2.rs:611-694: bf16 out == RNE(f32 out)."""
+    from fastvideo_rs_b200 import sdpa
+    q, k, v = (to_dev_bf16(x) for x in qkv(oracle, 7, 3, 300, 700))
+    o16 = sdpa.dense_fwd(q, k, v, out_bf16=True)
+    o32 = sdpa.dense_fwd(q, k, v, out_bf16=False)
+    assert torch.equal(o16, o32.to(torch.bfloat16))
+    # and two runs give the same bits
+    assert torch.equal(o16, sdpa.dense_fwd(q, k, v, out_bf16=True))
+
+
+def test_scale_argument(fvlib, oracle):
+    from fastvideo_rs_b200 import sdpa
+    q, k, v = qkv(oracle, 8, 2, 200, 300)
+    out = sdpa.dense_fwd(to_dev_bf16(q), to_dev_bf16(k), to_dev_bf16(v), scale=0.05)
+    assert_close(to_host_f32(out), oracle.sdpa_rows(q, k, v, scale=0.05), "scale 0.05")
+
+
+CAUSAL = [(2, 600, 600, 100, 0, 0), (2, 600, 600, 100, 2, 1), (2, 1000, 1000, 130, 0, 0), (1, 24, 24, 5, 2, 1),
+          (2, 2340, 2340, 780, 0, 0), (2, 54, 54, 6, 0, 0), (2, 54, 54, 18, 1, 0), (1, 700, 700, 256, 3, 0),
+          (1, 700, 700, 1, 0, 0), (1, 520, 520, 128, 0, 2)]
+
+
+@pytest.mark.parametrize("bh,sq,sk,bt,win,sink", CAUSAL)
+def test_block_causal_matches_masked_oracle(fvlib, oracle, bh, sq, sk, bt, win, sink):
+    """crates/fastvideo-gpucheck/src/kernels_wan.rs:89-364: the causal kernel against the masked
+    composed SDPA, including windows, sinks and blocks that do not divide the key tile."""
+    from fastvideo_rs_b200 import sdpa
+    q, k, v = qkv(oracle, 300 + bt + win, bh, sq, sk)
+    out = sdpa.dense_fwd(to_dev_bf16(q), to_dev_bf16(k), to_dev_bf16(v), causal=sdpa.BlockCausal(bt, win, sink))
+    assert sdpa.device_status() == 0
+    want = oracle.sdpa_rows(q, k, v, block_causal=(bt, win, sink))
+    assert_close(to_host_f32(out), want, f"causal bt{bt} w{win} s{sink}")
+
+
+def test_one_block_mask_is_dense(fvlib, oracle):
+    """kernels_wan.rs: a mask whose single block covers everything == the dense kernel, bit for bit."""
+    from fastvideo_rs_b200 import sdpa
+    q, k, v = (to_dev_bf16(x) for x in qkv(oracle, 9, 2, 500, 500))
+    a = sdpa.dense_fwd(q, k, v)
+    b = sdpa.dense_fwd(q, k, v, causal=sdpa.BlockCausal(500, 0, 0))
+    assert torch.equal(a, b)
+
+
+def test_entry_plans(fvlib, oracle):
+    """rt/sdpa.rs:508-575 on the device: each Plan the Wan caller builds runs and equals the oracle; plans
+    that belong to other kernels decline instead of falling back."""
+    from fastvideo_rs_b200 import Declined, sdpa
+    b, h, sq, sk = 2, 3, 260, 390
+    q, k, v = qkv(oracle, 11, b * h, sq, sk)
+    tq, tk, tv = (to_dev_bf16(x).view(b, h, -1, 128) for x in (q, k, v))
+    want = oracle.sdpa_rows(q, k, v)
+    assert_close(to_host_f32(sdpa.sdpa(tq, tk, tv, sdpa.Plan.dense(None))).reshape(b * h, sq, 128), want, "Plan.dense")
+    assert_close(to_host_f32(sdpa.sdpa(tq, tk, tv, sdpa.Plan.kv_window())).reshape(b * h, sq, 128), want, "Plan.kv_window")
+    want5 = oracle.sdpa_rows(q, k, v, scale=0.5)
+    assert_close(to_host_f32(sdpa.sdpa(tq, tk, tv, sdpa.Plan.dense(0.5))).reshape(b * h, sq, 128), want5, "scale 0.5")
+    bc = sdpa.BlockCausal(65, 0, 0)
+    wantc = oracle.sdpa_rows(q, k, v, block_causal=(65, 0, 0))
+    assert_close(to_host_f32(sdpa.sdpa(tq, tk, tv, sdpa.Plan.block_causal(None, bc))).reshape(b * h, sq, 128), wantc,
+                 "Plan.block_causal")
+    with pytest.raises(Declined):
+        sdpa.sdpa(tq, tk, tv, sdpa.Plan.composed(None, None))
+    with pytest.raises(Declined):
+        sdpa.sdpa(tq, tk, tv, sdpa.Plan.masked(None, torch.zeros(sq, sk, device="cuda")))
+    with pytest.raises(ValueError, match="BHSD"):
+        sdpa.sdpa(tq[0], tk[0], tv[0], sdpa.Plan.dense(None))
+
+
+def test_golden_tiny_wan_through_prep_and_attention(fvlib, oracle):
+    """Config 0 end to end against the committed fixture: projection -> RMSNorm (across heads) + RoPE ->
+    dense attention."""
+    import sys
+    sys.path.insert(0, str(ROOT / "tests" / "golden"))
+    import make_golden as M
+    from fastvideo_rs_b200 import wan
+    for name in ("wan_dense_tiny", "wan_causal_small"):
+        g = np.load(ROOT / "tests" / "golden" / f"{name}.npz")
+        grid, heads = tuple(int(x) for x in g["grid"]), int(g["heads"])
+        proj, w, seq, dim = M.wan_inputs(int(g["seed"]), 1, grid, heads)
+        causal = tuple(int(x) for x in g["causal"])
+        from fastvideo_rs_b200.sdpa import BlockCausal
+        attn = wan.WanSelfAttention(grid, heads, torch.from_numpy(w).cuda(), torch.from_numpy(w).cuda(),
+                                    causal=BlockCausal(*causal) if causal[0] else None)
+        out = attn.forward_self(to_dev_bf16(proj))
+        got = to_host_f32(out).reshape(heads, seq, 128)[:, g["rows"]]
+        assert_close(got, g["out"], name)
+
+
+def test_full_size_rows_wan_1p3b(fvlib, oracle):
+    """Config 1's self-attention shape (32 760 tokens) on 2 heads, sampled rows against the oracle, plus
+    size-independent properties at full size: rows are convex combinations of V (bounded by V's range),
+    and a constant V gives that constant."""
+    from fastvideo_rs_b200 import sdpa
+    bh, s = 2, 32760
+    q, k, v = qkv(oracle, 21, bh, s, s)
+    tq, tk, tv = to_dev_bf16(q), to_dev_bf16(k), to_dev_bf16(v)
+    out = sdpa.dense_fwd(tq, tk, tv)
+    assert sdpa.device_status() == 0
+    rows = sample_rows(s, 40, 3)
+    want = oracle.sdpa_rows(q, k, v, rows=rows)
+    assert_close(to_host_f32(out[:, torch.from_numpy(rows).long().cuda()]), want, "32760 rows")
+    assert float(out.float().abs().max()) <= float(tv.float().abs().max())
+    ones = torch.full_like(tv, 0.5)
+    const = sdpa.dense_fwd(tq, tk, ones)
+    assert torch.equal(const, ones)
+
+
+def test_cross_attention_shape(fvlib, oracle):
+    """Config 1's cross-attention: 32 760 queries over 512 text keys."""
+    from fastvideo_rs_b200 import sdpa
+    q, k, v = qkv(oracle, 22, 2, 32760, 512)
+    out = sdpa.dense_fwd(to_dev_bf16(q), to_dev_bf16(k), to_dev_bf16(v))
+    rows = sample_rows(32760, 64, 5)
+    assert_close(to_host_f32(out)[:, rows], oracle.sdpa_rows(q, k, v, rows=rows), "cross 32760x512")
+
+
+def test_two_pass_segments_equal_one_pass(fvlib, oracle):
+    """The sequence-parallel evaluation on one GPU: keys split into 3 uneven segments, pass 1 over the
+    middle one, pass 2 over the others merging pass 1 -- equals the oracle over all keys, and the
+    log-sum-exp it returns is the oracle's."""
+    from fastvideo_rs_b200 import sp
+    bh, sq, sk = 2, 333, 1000
+    q, k, v = qkv(oracle, 23, bh, sq, sk)
+    ranges = oracle.shard_ranges(sk, 3)  # (0,334) (334,333) (667,333)
+    rows = max(l for _, l in ranges)
+    k_all = np.zeros((3, bh, rows, 128), np.float32)
+    v_all = np.zeros_like(k_all)
+    for r, (s0, l) in enumerate(ranges):
+        k_all[r, :, :l] = k[:, s0 : s0 + l]
+        v_all[r, :, :l] = v[:, s0 : s0 + l]
+    tq, tk, tv = to_dev_bf16(q), to_dev_bf16(k_all), to_dev_bf16(v_all)
+    scale = 1.0 / math.sqrt(128)
+    o1 = torch.empty((bh, sq, 128), dtype=torch.float32, device="cuda")
+    lse1 = torch.empty((bh, sq), dtype=torch.float32, device="cuda")
+    mid = ranges[1]
+    sp.segments_fwd(tq, tk[1].contiguous(), tv[1].contiguous(), [mid[1]], [mid[0]], rows, scale, out=o1, lse_out=lse1)
+    lens = [ranges[0][1], 0, ranges[2][1]]
+    starts = [r[0] for r in ranges]
+    lse = torch.empty_like(lse1)
+    out = sp.segments_fwd(tq, tk, tv, lens, starts, rows, scale, prev_o=o1, prev_lse=lse1, lse_out=lse)
+    assert_close(to_host_f32(out), oracle.sdpa_rows(q, k, v), "two-pass")
+    # pass 1 alone is attention over the middle segment
+    assert_close(to_host_f32(o1), oracle.sdpa_rows(q, k[:, mid[0] : mid[0] + mid[1]], v[:, mid[0] : mid[0] + mid[1]]),
+                 "pass 1", 2e-3, 2e-4)
+    s = (q.astype(np.float64) @ k.astype(np.float64).transpose(0, 2, 1)) * scale
+    want_lse = (np.log(np.exp(s - s.max(-1, keepdims=True)).sum(-1)) + s.max(-1)) / math.log(2.0)
+    assert np.abs(to_host_f32(lse) - want_lse).max() < 2e-2
+
+
+def test_invalid_arguments_are_errors_not_launches(fvlib, oracle):
+    from fastvideo_rs_b200 import FvError, sdpa
+    q, k, v = (to_dev_bf16(x) for x in qkv(oracle, 24, 1, 64, 64))
+    with pytest.raises(FvError):
+        sdpa.dense_fwd(q, k, v, scale=-1.0)
+    with pytest.raises(ValueError):
+        sdpa.dense_fwd(q.float(), k, v)
+    with pytest.raises(ValueError):
+        sdpa.dense_fwd(q.cpu(), k.cpu(), v.cpu())
+
+
+def test_native_checker_passes(fvlib):
+    """The torch-free bring-up binary agrees (its own f64 host evaluation, NaN-poisoned outputs)."""
+    from fastvideo_rs_b200 import _build
+    exe = _build.build_native_checker()
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:]
