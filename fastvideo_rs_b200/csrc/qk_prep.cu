@@ -55,22 +55,24 @@ __global__ void __launch_bounds__(1024) fv_wan_qk_prep_kernel(const Params p) {
     const int row = blockIdx.x;     // b*seq + s
     const int b = row / p.seq, s = row % p.seq;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = blockDim.x >> 5;
-    const int h = (8 * t) / kD, pd = (8 * t) % kD;
+    // The block is rounded up to whole warps; threads past the row take part in the reductions only.
+    const bool act = t < p.heads * 16;
+    const int h = act ? (8 * t) / kD : 0, pd = act ? (8 * t) % kD : 0;
     const __nv_bfloat16* src = p.proj + (size_t)row * p.width;
     const size_t dst = (((size_t)b * p.heads + h) * p.seq + s) * kD + pd;
 
-    if (p.v_out) {
+    if (p.v_out && act) {
         const uint4 v = *reinterpret_cast<const uint4*>(src + p.col_v + 8 * t);
         *reinterpret_cast<uint4*>(p.v_out + dst) = v;
     }
-    float xq[8], xk[8];
+    float xq[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, xk[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float sq = 0.f, sk = 0.f;
-    if (p.q_out) {
+    if (p.q_out && act) {
         unpack8(*reinterpret_cast<const uint4*>(src + p.col_q + 8 * t), xq);
 #pragma unroll
         for (int i = 0; i < 8; i++) sq = __fadd_rn(sq, __fmul_rn(xq[i], xq[i]));
     }
-    if (p.k_out) {
+    if (p.k_out && act) {
         unpack8(*reinterpret_cast<const uint4*>(src + p.col_k + 8 * t), xk);
 #pragma unroll
         for (int i = 0; i < 8; i++) sk = __fadd_rn(sk, __fmul_rn(xk[i], xk[i]));
@@ -100,6 +102,7 @@ __global__ void __launch_bounds__(1024) fv_wan_qk_prep_kernel(const Params p) {
         sk = c;
         denom = (float)(p.heads * kD);
     }
+    if (!act) return;
     float cs[8], sn[8];
     if (p.cosv) {
         const float4* cp = reinterpret_cast<const float4*>(p.cosv + (size_t)s * kD + pd);
@@ -177,7 +180,7 @@ extern "C" int fv_wan_qk_prep_bf16(void* stream, const void* proj, int width, in
     p.col_v = col_v;
     p.eps = eps;
     p.per_head = norm_scope == FV_NORM_PER_HEAD;
-    const int threads = heads * 16;
+    const int threads = (heads * 16 + 31) & ~31;
     const size_t smem = 2 * (threads / 32 + 1) * sizeof(float);
     fvprep::fv_wan_qk_prep_kernel<<<(unsigned)(batch * seq), threads, smem, (cudaStream_t)stream>>>(p);
     FV_CUDA(cudaGetLastError());

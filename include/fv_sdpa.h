@@ -115,6 +115,41 @@ FV_API int fv_wan_qk_prep_bf16(void* stream, const void* proj, int width, int co
 FV_API int fv_wan_rope_tables(int ppf, int pph, int ppw, int d, double theta, int start_frame, float* cos_host,
                               float* sin_host);
 
+/* ---- video sparse attention (VSA) ------------------------------------------------------
+ * rt::vsa (crates/fastvideo-cudarc/src/rt/vsa.rs): TilePlan (:39-109), topk_for (:34-37),
+ * vsa_attention_device (:358-470) with its launchers (rt/ops.rs:811-923,1074-1383,1554-1619;
+ * rt/attn_dc.rs:275-604); arithmetic of the host twin vsa_attention_host (rt/vsa.rs:116-262). */
+
+/* topk_for: clamp(ceil((1 - sparsity) * num_tiles), 1, num_tiles). */
+FV_API int fv_vsa_topk_for(double sparsity, int num_tiles);
+
+/* TilePlan::new for a (T, H, W) grid of patch tokens: 4x4x4 cubes of 64 slots, partial cubes at the
+ * edges.  The plan is a host object; its tables are uploaded to the current device on first use. */
+FV_API int fv_vsa_plan_create(int gt, int gh, int gw, void** plan_out);
+FV_API int fv_vsa_plan_destroy(void* plan);
+/* num_tiles, seq = T*H*W, padded = num_tiles*64, tiles = cubes along (T, H, W); any may be null. */
+FV_API int fv_vsa_plan_info(void* plan, int* num_tiles, int* seq, int* padded, int tiles[3]);
+/* Host copies: slot_src [padded] (-1 = padding), token_slot [seq], block_sizes [num_tiles]; any may be null. */
+FV_API int fv_vsa_plan_host(void* plan, int32_t* slot_src, uint32_t* token_slot, uint32_t* block_sizes);
+/* Uploads the plan's tables to the current device now (otherwise the first forward does). */
+FV_API int fv_vsa_plan_upload(void* plan);
+/* Bytes of caller-owned device workspace fv_vsa_forward_bf16 needs for (bh, topk); 0 on bad arguments. */
+FV_API size_t fv_vsa_workspace_bytes(void* plan, int bh, int topk);
+
+/* One VSA attention call.  q, k, v [bh, seq, 128] bf16 (q, k already normed and rotated); gate
+ * [bh, seq, 128] bf16 or null (= ones): out = coarse * gate + fine, the reference's LINEAR gate
+ * (rt/vsa.rs:252-256) -- a caller that wants a sigmoid gate applies it to the gate tensor first.
+ * out [bh, seq, 128] bf16 or f32.  topk is clamped to [1, num_tiles].  workspace: device memory of at
+ * least fv_vsa_workspace_bytes, 256-byte aligned, private to this call until it completes.
+ * Optional device outputs for checks: selected_out u32 [bh, num_tiles, topk] (ASCENDING tile index;
+ * the same set the reference's host picks, which emits by descending score), scores_out f32
+ * [bh, num_tiles, num_tiles] (bit-identical to the host twin), coarse_out f32 [bh, num_tiles, 128].
+ * Declines: more than 4096 tiles, shared memory of the fine kernel beyond the device limit. */
+FV_API int fv_vsa_forward_bf16(void* stream, void* plan, const void* q, const void* k, const void* v,
+                               const void* gate, int bh, int topk, float scale, void* out, int out_is_bf16,
+                               void* workspace, size_t workspace_bytes, uint32_t* selected_out, float* scores_out,
+                               float* coarse_out);
+
 /* ---- the kernel-selection plugin ------------------------------------------------------
  * rt::sdpa_rule (crates/fastvideo-cudarc/src/rt/sdpa_rule.rs) as C: the Probe trait
  * (:321-350) becomes plain data, the enums keep their order, and one kernel is added:
