@@ -67,6 +67,33 @@ def segments_fwd(q, k_all, v_all, seg_len, seg_start, seg_rows, scale, *, out=No
     return out
 
 
+class SpLayout:
+    """Host-side bookkeeping of the exchange, pure Python: who holds which tokens, how the gathered
+    buffer is laid out ([world, bh, seg_rows, 128], shorter shards zero-padded to seg_rows), and the
+    segment tables of the two passes."""
+
+    def __init__(self, seq: int, world: int, rank: int):
+        if not 0 <= rank < max(world, 1):
+            raise ValueError(f"SP rank {rank} out of world {world}")
+        self.seq, self.world, self.rank = seq, max(world, 1), rank
+        self.ranges = shard_ranges(seq, self.world)
+        self.start, self.len = self.ranges[rank]
+        self.seg_rows = max(l for _, l in self.ranges)
+
+    def pass1(self):
+        """(seg_len, seg_start) of the local-keys pass: one segment, this rank's shard."""
+        return [self.len], [self.start]
+
+    def pass2(self):
+        """(seg_len, seg_start) of the remote-keys pass over the gathered buffer: every rank's segment at
+        its global offset, this rank's own one emptied (pass 1 covered it)."""
+        lens = [l if r != self.rank else 0 for r, (_, l) in enumerate(self.ranges)]
+        return lens, [s for s, _ in self.ranges]
+
+    def needs_padding(self) -> bool:
+        return self.len != self.seg_rows
+
+
 class SpAttention:
     """Sequence-parallel dense attention for one (seq, bh) shape; buffers allocated once."""
 
@@ -78,9 +105,9 @@ class SpAttention:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.seq, self.bh = seq, bh
-        self.ranges = shard_ranges(seq, self.world)
-        self.start, self.len = self.ranges[self.rank]
-        self.seg_rows = max(l for _, l in self.ranges)
+        self.layout = SpLayout(seq, self.world, self.rank)
+        self.ranges, self.start, self.len, self.seg_rows = (self.layout.ranges, self.layout.start, self.layout.len,
+                                                            self.layout.seg_rows)
         d = 128
         if self.world > 1:
             self.k_all = torch.zeros((self.world, bh, self.seg_rows, d), dtype=torch.bfloat16, device=self.device)
@@ -111,15 +138,15 @@ class SpAttention:
         ready.record(cur)
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ready)
-            self.dist.all_gather_into_tensor(self.k_all, ks, group=self.group)
-            self.dist.all_gather_into_tensor(self.v_all, vs, group=self.group)
+            self.dist.all_gather_into_tensor(self.k_all.view(-1, self.seg_rows, d), ks, group=self.group)
+            self.dist.all_gather_into_tensor(self.v_all.view(-1, self.seg_rows, d), vs, group=self.group)
             gathered = torch.cuda.Event()
             gathered.record(self.comm_stream)
         # pass 1: the local keys, while the exchange is in flight
-        segments_fwd(q, ks, vs, [self.len], [self.start], self.seg_rows, scale, out=self.o1, lse_out=self.lse1)
+        l1, s1 = self.layout.pass1()
+        segments_fwd(q, ks, vs, l1, s1, self.seg_rows, scale, out=self.o1, lse_out=self.lse1)
         cur.wait_event(gathered)
         # pass 2: every other rank's keys, merged with pass 1
-        lens = [l if r != self.rank else 0 for r, (_, l) in enumerate(self.ranges)]
-        starts = [s for s, _ in self.ranges]
-        return segments_fwd(q, self.k_all, self.v_all, lens, starts, self.seg_rows, scale, out=out,
+        l2, s2 = self.layout.pass2()
+        return segments_fwd(q, self.k_all, self.v_all, l2, s2, self.seg_rows, scale, out=out,
                             prev_o=self.o1, prev_lse=self.lse1)

@@ -1,0 +1,46 @@
+"""One rank of the multi-GPU sequence-parallel check (run under torch.distributed.run by
+tests/test_gpu_sp_multi.py): this rank's output rows against the CPU oracle over ALL keys."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+
+def main():
+    seq = int(sys.argv[1]) if len(sys.argv) > 1 else 3001
+    bh = int(sys.argv[2]) if len(sys.argv) > 2 else 3
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from fastvideo_rs_b200 import sdpa, sp
+    from oracle import oracle as O
+    q, k, v = (O.bf16_round(O.seeded_normal(61, i, (bh, seq, 128))) for i in range(3))
+    dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to("cuda", torch.bfloat16)
+    attn = sp.SpAttention(seq, bh)
+    s0, n = attn.start, attn.len
+    out = None
+    for _ in range(2):  # twice: the gather buffers are reused
+        out = attn.forward(dev(q[:, s0:s0 + n]), dev(k[:, s0:s0 + n]), dev(v[:, s0:s0 + n]))
+    torch.cuda.synchronize()
+    assert sdpa.device_status() == 0
+    rows = np.unique(np.concatenate([np.arange(s0, s0 + min(n, 40)), np.arange(s0 + max(n - 40, 0), s0 + n)])).astype(np.int32)
+    want = O.sdpa_rows(q, k, v, rows=rows)
+    got = out.float().cpu().numpy()[:, rows - s0]
+    err = np.abs(got - want)
+    ok = bool(err.max() <= 2e-2 and err.mean() <= 2e-3 and np.isfinite(got).all())
+    flag = torch.tensor([0 if ok else 1], device="cuda")
+    dist.all_reduce(flag)
+    print(f"rank {rank}/{world}: rows {s0}..{s0 + n} max-abs {err.max():.3e} mean-abs {err.mean():.3e} {'ok' if ok else 'FAIL'}",
+          flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag.item()) == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,23 @@
+"""Sequence-parallel attention across real GPUs (NCCL all-gather of K/V overlapped with the local pass).
+Needs at least two B200s in the box; skipped otherwise."""
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.mark.parametrize("seq", [3001, 4096])
+def test_sp_matches_oracle_on_all_gpus(fvlib, oracle, seq):
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("one GPU in this box")
+    world = 8 if n >= 8 else (4 if n >= 4 else 2)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", "29631", str(ROOT / "tests" / "sp_worker.py"), str(seq), "3"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env={**__import__("os").environ, "NCCL_NVLS_ENABLE": "0"})
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]

@@ -1,0 +1,118 @@
+"""The sequence-parallel path's host logic on CPU ranks (gloo, world size 2 and 3): shard ranges, the
+padded all-gather layout, the two passes' segment tables and the log-sum-exp merge.  The attention of
+each pass is evaluated by a numpy stand-in that follows the kernel's segment contract
+(include/fv_sdpa.h, fv_sdpa_segments_bf16), so what is checked is everything around the kernel."""
+import math
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+
+def segments_attention_np(q, k_all, v_all, seg_len, seg_start, scale, prev=None):
+    """Softmax attention of q [bh, sq, d] over the listed segments of k_all / v_all [nseg, bh, rows, d];
+    returns (normalised out f32, lse in the base-2 domain).  prev = (out, lse) of another key set merges."""
+    bh, sq, d = q.shape
+    ks, vs = [], []
+    for s, n in enumerate(seg_len):
+        ks.append(k_all[s, :, :n])
+        vs.append(v_all[s, :, :n])
+    k, v = np.concatenate(ks, axis=1).astype(np.float64), np.concatenate(vs, axis=1).astype(np.float64)
+    sc = (q.astype(np.float64) @ k.transpose(0, 2, 1)) * scale * math.log2(math.e)
+    m = sc.max(-1, keepdims=True)
+    p = np.exp2(sc - m)
+    l = p.sum(-1, keepdims=True)
+    out, lse = (p @ v) / l, (m + np.log2(l))[..., 0]
+    if prev is not None:
+        po, pl = prev
+        M = np.maximum(lse, pl)
+        wn, wp = np.exp2(lse - M), np.exp2(pl - M)
+        out = (out * wn[..., None] + po * wp[..., None]) / (wn + wp)[..., None]
+        lse = M + np.log2(wn + wp)
+    return out, lse
+
+
+def worker(rank, world, seq, port, q_out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fastvideo_rs_b200 import sp
+        from oracle import oracle as O
+        bh, d = 2, 16
+        q, k, v = (O.bf16_round(O.seeded_normal(5, i, (bh, seq, d))) for i in range(3))
+        lay = sp.SpLayout(seq, world, rank)
+        assert lay.ranges == O.shard_ranges(seq, world)
+        ql = sp.shard_tensor(torch.from_numpy(q), 1, rank, world).numpy()
+        kl = sp.shard_tensor(torch.from_numpy(k), 1, rank, world).numpy()
+        vl = sp.shard_tensor(torch.from_numpy(v), 1, rank, world).numpy()
+        assert ql.shape[1] == lay.len
+        # the exchange: zero-padded shards gathered rank-major, exactly the layout the kernel indexes
+        pad = lambda x: np.concatenate([x, np.zeros((bh, lay.seg_rows - x.shape[1], d), np.float32)], axis=1)
+        k_all = torch.zeros((world, bh, lay.seg_rows, d))
+        v_all = torch.zeros((world, bh, lay.seg_rows, d))
+        dist.all_gather_into_tensor(k_all.view(world * bh, lay.seg_rows, d), torch.from_numpy(pad(kl)))
+        dist.all_gather_into_tensor(v_all.view(world * bh, lay.seg_rows, d), torch.from_numpy(pad(vl)))
+        scale = 1.0 / math.sqrt(d)
+        l1, s1 = lay.pass1()
+        assert l1 == [lay.len] and s1 == [lay.start]
+        o1 = segments_attention_np(ql, pad(kl)[None], pad(vl)[None], l1, s1, scale)
+        l2, s2 = lay.pass2()
+        assert l2[rank] == 0 and sum(l2) == seq - lay.len and s2 == [s for s, _ in lay.ranges]
+        keep = [r for r in range(world) if l2[r] > 0]
+        out, _ = segments_attention_np(ql, k_all.numpy()[keep], v_all.numpy()[keep], [l2[r] for r in keep],
+                                       [s2[r] for r in keep], scale, prev=o1)
+        rows = np.arange(lay.start, lay.start + lay.len, dtype=np.int32)
+        want = O.sdpa_rows(q, k, v, scale=scale, rows=rows)
+        err = float(np.abs(out - want).max())
+        # outputs stay sharded; gathering them reproduces the full result (sp::all_gather_seq)
+        outs = [torch.zeros((bh, lay.seg_rows, d), dtype=torch.float64) for _ in range(world)]
+        mine = torch.zeros((bh, lay.seg_rows, d), dtype=torch.float64)
+        mine[:, : lay.len] = torch.from_numpy(out)
+        dist.all_gather(outs, mine)
+        full = sp.all_gather_seq([o[:, :l] for o, (_, l) in zip(outs, lay.ranges)], 1).numpy()
+        err_full = float(np.abs(full - O.sdpa_rows(q, k, v, scale=scale)).max())
+        q_out.put((rank, err, err_full))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,seq", [(2, 11), (2, 64), (3, 100)])
+def test_two_pass_sp_on_gloo_ranks(fvlib, oracle, world, seq):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + world * 7 + seq) % 2000
+    procs = [ctx.Process(target=worker, args=(r, world, seq, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=90) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(r for r, _, _ in res) == list(range(world))
+    for r, err, err_full in res:
+        assert err < 1e-5 and err_full < 1e-5, (r, err, err_full)
+
+
+def test_layout_tables(fvlib):
+    from fastvideo_rs_b200 import sp
+    lay = sp.SpLayout(75600, 8, 3)
+    assert (lay.start, lay.len, lay.seg_rows) == (28350, 9450, 9450) and not lay.needs_padding()
+    lay = sp.SpLayout(11, 2, 1)
+    assert (lay.start, lay.len, lay.seg_rows) == (6, 5, 6) and lay.needs_padding()
+    assert lay.pass2() == ([6, 0], [0, 6])
+    with pytest.raises(ValueError):
+        sp.SpLayout(10, 2, 2)
+    x = torch.arange(12.0).reshape(1, 1, 4, 3)
+    parts = [sp.shard_tensor(x, 2, r, 2) for r in range(2)]
+    assert torch.equal(sp.all_gather_seq(parts, 2), x)
+    with pytest.raises(ValueError):
+        sp.all_gather_seq([], 2)
