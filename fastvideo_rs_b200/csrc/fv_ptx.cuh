@@ -187,4 +187,50 @@ FV_DEV uint32_t pack_bf16x2(float lo, float hi) {
     return r;
 }
 
+// Packed pairs of f32 (sm_100 has two-wide FADD / FMUL / FFMA on 64-bit register pairs).
+FV_DEV uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+FV_DEV void unpack_f32x2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+FV_DEV uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+FV_DEV uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+FV_DEV float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// 2^x for a pair, on the FMA pipe (no MUFU): x = n + f with n = round(x), f in [-0.5, 0.5];
+// 2^f by a cubic fitted to a relative error of 7.5e-5 (far inside the bf16 rounding of P, 3.9e-3);
+// 2^n by adding n to the exponent field.  x is clamped to -126 (result ~1e-38, never a denormal path).
+FV_DEV void ex2_poly_x2(float x0, float x1, float& p0, float& p1) {
+    const float MAGIC = 12582912.f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+    x0 = fmaxf(x0, -126.f);
+    x1 = fmaxf(x1, -126.f);
+    const uint64_t x = pack_f32x2(x0, x1);
+    const uint64_t r = add_f32x2(x, pack_f32x2(MAGIC, MAGIC));
+    float r0, r1;
+    unpack_f32x2(r, r0, r1);
+    const uint64_t rn = add_f32x2(r, pack_f32x2(-MAGIC, -MAGIC));
+    // f = x - round(x)
+    const uint64_t f = fma_f32x2(rn, pack_f32x2(-1.f, -1.f), x);
+    uint64_t p = fma_f32x2(f, pack_f32x2(0.055171408f, 0.055171408f), pack_f32x2(0.24261075f, 0.24261075f));
+    p = fma_f32x2(p, f, pack_f32x2(0.69326097f, 0.69326097f));
+    p = fma_f32x2(p, f, pack_f32x2(0.9999281f, 0.9999281f));
+    float q0, q1;
+    unpack_f32x2(p, q0, q1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
+}
+
 }  // namespace fvp

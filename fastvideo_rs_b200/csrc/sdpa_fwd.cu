@@ -2,18 +2,48 @@
 #include "sdpa_fwd.cuh"
 #include "fv_runtime.h"
 #include <math.h>
+#include <stdlib.h>
 
 namespace fvsdpa {
 
 constexpr int kStages = 4;
 
+// One entry per softmax variant (see sdpa_body); FV_SDPA_VARIANT picks one at run time for A/B timing,
+// kDefaultVariant otherwise.
+template <int VAR>
 __global__ void __launch_bounds__(kThreads, 1)
 fv_sdpa_fwd_d128(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                  const __grid_constant__ CUtensorMap tv, const __grid_constant__ Params p) {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL)
     extern __shared__ __align__(1024) unsigned char fv_smem[];
-    sdpa_body<kStages>(&tq, &tk, &tv, p, fv_smem);
+    sdpa_body<kStages, VAR>(&tq, &tk, &tv, p, fv_smem);
 #endif
+}
+
+constexpr int kDefaultVariant = 0;
+typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const Params);
+static KernelFn kernel_for(int var) {
+    switch (var) {
+        case 1: return fv_sdpa_fwd_d128<1>;
+        case 3: return fv_sdpa_fwd_d128<3>;
+        case 5: return fv_sdpa_fwd_d128<5>;
+        case 8: return fv_sdpa_fwd_d128<8>;
+        case 9: return fv_sdpa_fwd_d128<9>;
+        case 11: return fv_sdpa_fwd_d128<11>;
+        case 13: return fv_sdpa_fwd_d128<13>;
+        case 2: return fv_sdpa_fwd_d128<2>;
+        case 10: return fv_sdpa_fwd_d128<10>;
+        default: return fv_sdpa_fwd_d128<0>;
+    }
+}
+static int chosen_variant() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("FV_SDPA_VARIANT");
+        v = e ? atoi(e) : kDefaultVariant;
+        if (v < 0 || v > 15) v = kDefaultVariant;
+    }
+    return v;
 }
 
 static int launch(cudaStream_t stream, const void* q, const void* k, const void* v, void* out, int out_is_bf16, int bh,
@@ -84,13 +114,15 @@ static int launch(cudaStream_t stream, const void* q, const void* k, const void*
         if (rc != FV_RAN) return rc;
     }
 
-    static bool attr_set[64] = {};
+    static bool attr_set[64][16] = {};
     constexpr uint32_t smem = smem_bytes<kStages>();
-    if (!attr_set[dev]) {
-        FV_CUDA(cudaFuncSetAttribute(fv_sdpa_fwd_d128, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set[dev] = true;
+    const int var = chosen_variant();
+    const KernelFn fn = kernel_for(var);
+    if (!attr_set[dev][var]) {
+        FV_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[dev][var] = true;
     }
-    fv_sdpa_fwd_d128<<<(unsigned)grid, kThreads, smem, stream>>>(tq, tk, tv, p);
+    fn<<<(unsigned)grid, kThreads, smem, stream>>>(tq, tk, tv, p);
     FV_CUDA(cudaGetLastError());
     return FV_RAN;
 }

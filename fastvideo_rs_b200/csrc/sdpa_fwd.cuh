@@ -110,7 +110,61 @@ FV_DEV void issue_pv(uint32_t tO, uint32_t tP, uint32_t sV, bool acc) {
 FV_DEV float u2f(uint32_t u) { return __uint_as_float(u); }
 FV_DEV uint32_t f2u(float f) { return __float_as_uint(f); }
 
-template <int NS>
+// P = 2^(s*sl2 + noff) for the 128 scores of one row: bf16 pairs stored to TMEM at tP, returns the f32 row sum.
+// PACK: two-wide FMA / ADD.  PMASK >= 0: the pairs w of each half with (w & PMASK) == PMASK go through the
+// FMA-pipe exponential (1 -> every second pair, 3 -> every fourth), the others through MUFU ex2.
+template <bool PACK, int PMASK>
+FV_DEV float exp_and_store(uint32_t (&u)[128], float sl2, float noff, uint32_t tP) {
+    using namespace fvp;
+    float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+    uint64_t ya = pack_f32x2(0.f, 0.f), yb = pack_f32x2(0.f, 0.f);
+    const uint64_t sl2x = pack_f32x2(sl2, sl2), noffx = pack_f32x2(noff, noff);
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        uint32_t pw[32];
+#pragma unroll
+        for (int w = 0; w < 32; w++) {
+            const int c = 64 * h + 2 * w;
+            float t0, t1, p0, p1;
+            if constexpr (PACK) {
+                unpack_f32x2(fma_f32x2(pack_f32x2(u2f(u[c]), u2f(u[c + 1])), sl2x, noffx), t0, t1);
+            } else {
+                t0 = fmaf(u2f(u[c]), sl2, noff);
+                t1 = fmaf(u2f(u[c + 1]), sl2, noff);
+            }
+            if constexpr (PMASK >= 0) {
+                if ((w & PMASK) == PMASK) {
+                    ex2_poly_x2(t0, t1, p0, p1);
+                } else {
+                    p0 = ex2(t0);
+                    p1 = ex2(t1);
+                }
+            } else {
+                p0 = ex2(t0);
+                p1 = ex2(t1);
+            }
+            if constexpr (PACK) {
+                if (w & 1) yb = add_f32x2(yb, pack_f32x2(p0, p1));
+                else ya = add_f32x2(ya, pack_f32x2(p0, p1));
+            } else {
+                if (w & 1) { y2 += p0; y3 += p1; }
+                else { y0 += p0; y1 += p1; }
+            }
+            pw[w] = pack_bf16x2(p0, p1);
+        }
+        tmem_st32(tP + 32u * h, pw);
+    }
+    if constexpr (PACK) {
+        unpack_f32x2(ya, y0, y1);
+        unpack_f32x2(yb, y2, y3);
+    }
+    return (y0 + y1) + (y2 + y3);
+}
+
+// VAR bits: 1 = packed f32x2 scale-and-subtract and row sum; 2 = half of the exponentials of an unmasked
+// tile on the FMA pipe (pairs 1, 3, 5, ... of each group of four columns); 4 = a quarter of them instead;
+// 8 = three-input max.
+template <int NS, int VAR>
 FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtensorMap* tv, const Params& p,
                       unsigned char* smem_raw) {
     using namespace fvp;
@@ -212,22 +266,40 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
             const int c_lo = min(max(r_lo - k0, 0), lim);
             const int c_hi = min(max(r_hi - k0, 0), lim);
             const int c_sink = min(max(r_sink - k0, 0), lim);
-            if (!((c_lo == 0 && c_hi == kBN) || c_sink == kBN)) {
+            const bool full_tile = (c_lo == 0 && c_hi == kBN) || c_sink == kBN;
+            if (!full_tile) {
 #pragma unroll
                 for (int c = 0; c < 128; c++) {
                     const bool vis = (c >= c_lo && c < c_hi) || c < c_sink;
                     u[c] = vis ? u[c] : f2u(NEG);
                 }
             }
-            float x0 = u2f(u[0]), x1 = u2f(u[1]), x2 = u2f(u[2]), x3 = u2f(u[3]);
+            float tmax;
+            if constexpr ((VAR & 8) != 0) {
+                float x0 = max3(u2f(u[0]), u2f(u[1]), u2f(u[2])), x1 = max3(u2f(u[3]), u2f(u[4]), u2f(u[5]));
+                float x2 = max3(u2f(u[6]), u2f(u[7]), u2f(u[8])), x3 = max3(u2f(u[9]), u2f(u[10]), u2f(u[11]));
 #pragma unroll
-            for (int c = 4; c < 128; c += 4) {
-                x0 = fmaxf(x0, u2f(u[c]));
-                x1 = fmaxf(x1, u2f(u[c + 1]));
-                x2 = fmaxf(x2, u2f(u[c + 2]));
-                x3 = fmaxf(x3, u2f(u[c + 3]));
+                for (int c = 12; c < 124; c += 8) {
+                    x0 = max3(x0, u2f(u[c]), u2f(u[c + 1]));
+                    x1 = max3(x1, u2f(u[c + 2]), u2f(u[c + 3]));
+                    x2 = max3(x2, u2f(u[c + 4]), u2f(u[c + 5]));
+                    x3 = max3(x3, u2f(u[c + 6]), u2f(u[c + 7]));
+                }
+                x0 = max3(x0, u2f(u[124]), u2f(u[125]));
+                x1 = max3(x1, u2f(u[126]), u2f(u[127]));
+                tmax = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
+            } else {
+                float x0 = u2f(u[0]), x1 = u2f(u[1]), x2 = u2f(u[2]), x3 = u2f(u[3]);
+#pragma unroll
+                for (int c = 4; c < 128; c += 4) {
+                    x0 = fmaxf(x0, u2f(u[c]));
+                    x1 = fmaxf(x1, u2f(u[c + 1]));
+                    x2 = fmaxf(x2, u2f(u[c + 2]));
+                    x3 = fmaxf(x3, u2f(u[c + 3]));
+                }
+                tmax = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
             }
-            const float tm2 = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3)) * sl2;
+            const float tm2 = tmax * sl2;
             const bool grow = tm2 > m + kLazyLog2;
             float a = 1.f;
             if (grow) {
@@ -249,26 +321,15 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
                     tmem_st32(tO + 32u * q, o);
                 }
             }
-            float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                uint32_t pw[32];
-#pragma unroll
-                for (int w = 0; w < 32; w += 2) {
-                    const float p0 = ex2(fmaf(u2f(u[64 * h + 2 * w]), sl2, -off));
-                    const float p1 = ex2(fmaf(u2f(u[64 * h + 2 * w + 1]), sl2, -off));
-                    const float p2 = ex2(fmaf(u2f(u[64 * h + 2 * w + 2]), sl2, -off));
-                    const float p3 = ex2(fmaf(u2f(u[64 * h + 2 * w + 3]), sl2, -off));
-                    y0 += p0;
-                    y1 += p1;
-                    y2 += p2;
-                    y3 += p3;
-                    pw[w] = pack_bf16x2(p0, p1);
-                    pw[w + 1] = pack_bf16x2(p2, p3);
-                }
-                tmem_st32(tP + 32u * h, pw);
-            }
-            l = fmaf(l, a, (y0 + y1) + (y2 + y3));
+            const float noff = -off;
+            constexpr int kPolyMask = (VAR & 2) ? 1 : ((VAR & 4) ? 3 : -1);
+            // the FMA-pipe exponential never returns an exact zero: masked tiles keep the MUFU path
+            float rowsum;
+            // (warp-uniform choice: the TMEM store inside is warp-collective and must not sit in divergent code)
+            if (kPolyMask >= 0 && __all_sync(0xffffffffu, full_tile))
+                rowsum = exp_and_store<(VAR & 1) != 0, kPolyMask>(u, sl2, noff, tP);
+            else rowsum = exp_and_store<(VAR & 1) != 0, -1>(u, sl2, noff, tP);
+            l = fmaf(l, a, rowsum);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(b_p + 8 * tile);
