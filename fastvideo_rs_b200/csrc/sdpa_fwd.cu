@@ -49,7 +49,7 @@ static int chosen_variant() {
 static int launch(cudaStream_t stream, const void* q, const void* k, const void* v, void* out, int out_is_bf16, int bh,
                   int sq, int nseg, const int* seg_len, const int* seg_start, int seg_rows, float scale, int mask_mode,
                   int block_tokens, int window, int sink, int q_row0, float* lse_out, const float* prev_o,
-                  const float* prev_lse) {
+                  const float* prev_lse, int* status_in = nullptr) {
     int dev;
     int rc = fvrt::require_sm100(&dev);
     if (rc != FV_RAN) return rc;
@@ -94,8 +94,12 @@ static int launch(cudaStream_t stream, const void* q, const void* k, const void*
     p.sink = sink;
     p.q_row0 = q_row0;
     p.heavy_first = mask_mode == FV_MASK_BLOCK_CAUSAL;
-    rc = fvrt::status_word(dev, &p.status);
-    if (rc != FV_RAN) return rc;
+    if (status_in) {
+        p.status = status_in;
+    } else {
+        rc = fvrt::status_word(dev, &p.status);
+        if (rc != FV_RAN) return rc;
+    }
 
     const long long grid = (long long)p.nqb * bh;
     if (grid > 0x7fffffffll) return FV_DECLINED;
@@ -127,7 +131,72 @@ static int launch(cudaStream_t stream, const void* q, const void* k, const void*
     return FV_RAN;
 }
 
+// ---- built-in scratch for callers that cannot allocate ---------------------------------------------
+// 256 bytes of status block, then the pass-1 result of the two-pass evaluation: kNoAllocMaxRows rows of
+// 128 f32 and one f32 log-sum-exp per row.  Held by every GPU that loads the library until the process
+// exits (about 32 MiB).
+constexpr long long kNoAllocMaxRows = 65024;
+constexpr size_t kNoAllocFloats = 64 + (size_t)kNoAllocMaxRows * (kD + 1);
+static __device__ __align__(256) float fv_noalloc_scratch[kNoAllocFloats];
+// In host code the array's name is only a stand-in: the device address comes from the runtime, once per
+// device, with that device current.
+static float* g_noalloc_ptr[64] = {};
+
+static int noalloc_base(int dev, float** out) {
+    if (!g_noalloc_ptr[dev]) {
+        float* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&ptr, fv_noalloc_scratch);
+        if (e != cudaSuccess || !ptr)
+            return fvrt::fail(FV_ERR_CUDA, "cudaGetSymbolAddress(fv_noalloc_scratch) on device %d: %s", dev,
+                              cudaGetErrorString(e));
+        g_noalloc_ptr[dev] = ptr;
+    }
+    *out = g_noalloc_ptr[dev];
+    return FV_RAN;
+}
+
+static int two_pass_noalloc(cudaStream_t stream, const void* q, const void* k_local, const void* v_local, int local_len,
+                            int local_start, int local_rows, const void* k_all, const void* v_all, int nseg,
+                            const int* seg_len, const int* seg_start, int seg_rows, void* out, int out_is_bf16, int bh,
+                            int sq, float scale, cudaEvent_t remote_ready) {
+    int dev;
+    int rc = fvrt::require_sm100(&dev);
+    if (rc != FV_RAN) return rc;
+    const long long rows = (long long)bh * sq;
+    if (rows > kNoAllocMaxRows)
+        return fvrt::fail(FV_ERR_INVALID,
+                          "sdpa two-pass (no allocation): bh*sq = %lld rows, the built-in scratch holds %lld; use "
+                          "fv_sdpa_segments_bf16 with buffers of your own for larger calls", rows, kNoAllocMaxRows);
+    float* base;
+    rc = noalloc_base(dev, &base);
+    if (rc != FV_RAN) return rc;
+    int* status = reinterpret_cast<int*>(base);
+    float* o1 = base + 64;
+    float* lse1 = o1 + (size_t)kNoAllocMaxRows * kD;
+    // The scratch keeps what the previous call left: the status word has to start at zero.
+    FV_CUDA(cudaMemsetAsync(status, 0, 256, stream));
+    rc = launch(stream, q, k_local, v_local, o1, 0, bh, sq, 1, &local_len, &local_start, local_rows, scale, FV_MASK_NONE,
+                0, 0, 0, 0, lse1, nullptr, nullptr, status);
+    if (rc != FV_RAN) return rc;
+    if (remote_ready) FV_CUDA(cudaStreamWaitEvent(stream, remote_ready, 0));
+    return launch(stream, q, k_all, v_all, out, out_is_bf16, bh, sq, nseg, seg_len, seg_start, seg_rows, scale,
+                  FV_MASK_NONE, 0, 0, 0, 0, nullptr, o1, lse1, status);
+}
+
 }  // namespace fvsdpa
+
+extern "C" int fv_sdpa_two_pass_noalloc_bf16(void* stream, const void* q, const void* k_local, const void* v_local,
+                                             int local_len, int local_start, int local_rows, const void* k_all,
+                                             const void* v_all, int nseg, const int* seg_len, const int* seg_start,
+                                             int seg_rows, void* out, int out_is_bf16, int bh, int sq, float scale,
+                                             void* remote_ready_event) {
+    fvrt::clear_error();
+    if (bh <= 0 || sq <= 0 || nseg <= 0 || seg_rows <= 0 || local_rows <= 0) return FV_DECLINED;
+    if (!seg_len || !seg_start) return fvrt::fail(FV_ERR_INVALID, "sdpa: null segment table");
+    return fvsdpa::two_pass_noalloc((cudaStream_t)stream, q, k_local, v_local, local_len, local_start, local_rows, k_all,
+                                    v_all, nseg, seg_len, seg_start, seg_rows, out, out_is_bf16, bh, sq, scale,
+                                    (cudaEvent_t)remote_ready_event);
+}
 
 extern "C" int fv_sdpa_segments_bf16(void* stream, const void* q, const void* k, const void* v, void* out,
                                      int out_is_bf16, int bh, int sq, int nseg, const int* seg_len,

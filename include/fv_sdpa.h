@@ -90,6 +90,33 @@ FV_API int fv_sdpa_segments_bf16(void* stream, const void* q, const void* k, con
                           float scale, int mask_mode, int block_tokens, int window, int sink, int q_row0,
                           float* lse_out, const float* prev_o, const float* prev_lse);
 
+/* Two-pass attention without any allocation -- no counterpart in the reference.
+ *
+ * For hosts that may not allocate device memory where they call attention: a serving loop with a fixed
+ * memory budget, a real-time thread that must not take the allocator's device-wide synchronisation, a
+ * runtime whose buffers all come from a pool sized at start-up.  The other entry points need scratch from
+ * somewhere (the library's status word comes from cudaMalloc on a device's first call; the pass-1 result of
+ * a two-pass evaluation is a caller buffer).  This one computes the same thing as fv_sdpa_segments_bf16
+ * called twice -- pass 1 over the local keys (k_local / v_local: one segment of local_len keys starting at
+ * global index local_start, local_rows rows per head in memory), pass 2 over the gathered segments
+ * (k_all / v_all as in fv_sdpa_segments_bf16; give the local segment length 0 there) merging pass 1 -- and
+ * keeps the status word and the pass-1 result (f32 [bh, sq, 128] + [bh, sq]) in a fixed array inside the
+ * library.  It calls no cudaMalloc, cudaFree or other allocating routine.
+ *   Limit: bh * sq <= 65 024 rows (the array is about 32 MiB per GPU, held until the process exits);
+ *     larger calls return FV_ERR_INVALID with the numbers in fv_last_error().
+ *   remote_ready_event: optional cudaEvent_t; pass 2 waits for it on `stream` (record it after the K/V
+ *     all-gather on the communication stream), so pass 1 overlaps the exchange.
+ *   The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current); make that first call before any stream capture.
+ *   Every call uses the same array: the status word is cleared at the start of each call, the pass-1 area
+ *     is overwritten.  Calls that overlap on one GPU (two streams, two threads) race on it -- serialise them.
+ *   Dense only (no mask). */
+FV_API int fv_sdpa_two_pass_noalloc_bf16(void* stream, const void* q, const void* k_local, const void* v_local,
+                                         int local_len, int local_start, int local_rows, const void* k_all,
+                                         const void* v_all, int nseg, const int* seg_len, const int* seg_start,
+                                         int seg_rows, void* out, int out_is_bf16, int bh, int sq, float scale,
+                                         void* remote_ready_event);
+
 /* ---- Wan q/k prologue -------------------------------------------------------------
  * Replaces the two CudaTensor::qk_norm_rope_bhsd launches and the split_heads_bhsd launch of
  * WanAttention::forward_self (crates/fastvideo-cudarc/src/wan/transformer.rs:163-178,287-289;
