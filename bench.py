@@ -39,9 +39,12 @@ WORKLOADS = {
     "wan14b_720p_dense": dict(batch=1, heads=40, grid=(21, 45, 80), block=0, desc="Wan2.1-14B 720p x81f dense self-attention"),
     "wan1p3b_480p_dense": dict(batch=2, heads=12, grid=(21, 30, 52), block=0, desc="Wan2.1-1.3B 480p x81f dense self-attention, CFG pair"),
     "wan1p3b_480p_causal": dict(batch=1, heads=12, grid=(21, 30, 52), block=4680, desc="Self-Forcing chunk-causal (7 chunks x 3 frames) at the Wan-1.3B shape"),
+    "wan1p3b_480p_vsa": dict(batch=1, heads=12, grid=(21, 30, 52), block=0, vsa_topk=78,
+                             desc="VSA block-sparse self-attention at the Wan-1.3B 480p grid: 624 tiles of 64 tokens, top-k 78 (12.5 %), "
+                                  "sigmoid gate applied to seeded logits before the call"),
     "tiny": dict(batch=1, heads=12, grid=(3, 8, 8), block=0, desc="tiny Wan-arch dense self-attention (192 tokens)"),
 }
-METRIC = "Wan self-attn TFLOP/s (dense, prologue + attention), whole job"
+METRIC = "Wan self-attn TFLOP/s (prologue + attention), whole job"
 
 
 def peaks():
@@ -179,12 +182,22 @@ def main():
     seq = grid[0] * grid[1] * grid[2]
     dim = heads * 128
     total_flops = 4.0 * batch * heads * visible_pairs(seq, block) * 128
+    vsa_topk = wl.get("vsa_topk", 0)
+    if vsa_topk:
+        # the reference's count for the fine stage (padded slots, crates/fastvideo-gpucheck/src/kernels/vsa_dc.rs:648)
+        # plus the coarse tile attention
+        ntile = math.prod(-(-g // 4) for g in grid)
+        total_flops = 4.0 * batch * heads * (ntile * 64.0) * (vsa_topk * 64.0) * 128 + 4.0 * batch * heads * ntile * ntile * 128
     cfg = dict(workload=f"{args.workload}: {wl['desc']}; b{batch} h{heads} S{seq} d128", seed=args.seed,
                l2="inputs exceed L2 (no flush needed)" if batch * seq * dim * 2 * 3 > 2 * 126e6 else "L2 flushed between steps",
                parallelism=f"sp{world}" if world > 1 else "single")
 
     if args.impl == "reference":
         if rank != 0:
+            return
+        if vsa_topk:
+            print(json.dumps(dict(impl="reference", unavailable="the VSA workload's CPU arm is the oracle's vsa_attention_host, timed by "
+                                  "tests only; run --impl reference on a dense workload")))
             return
         # whole --steps/--warmup run of bounded samples
         args.steps_cpu, args.warmup_cpu = max(1, min(args.steps, 3)), min(args.warmup, 1)
@@ -224,12 +237,32 @@ def main():
     causal = sdpa.BlockCausal(block, 0, 0) if block else None
     if world > 1 and causal is not None:
         raise SystemExit("the chunk-causal workload is single-GPU in this bench")
+    if vsa_topk and world > 1:
+        raise SystemExit("the VSA workload is single-GPU in this bench")
     spa = sp.SpAttention(seq, bh, device=dev) if world > 1 else None
+    vsa_in = None
+    if vsa_topk:
+        from fastvideo_rs_b200 import vsa
+        vctx = vsa.VsaCtx(grid, topk=vsa_topk)
+        mk = lambda: torch.randn((bh, seq, 128), generator=gen, device=dev, dtype=torch.float32)
+        vq, vk, vv = (mk().to(torch.bfloat16) for _ in range(3))
+        vgate = torch.sigmoid(mk()).to(torch.bfloat16)
+        vsa_in = torch.stack([vq, vk, vv, vgate])  # one tensor so the end-to-end leg copies it in one go
+        proj = vsa_in
     out_buf = torch.empty((bh, length, 128), dtype=torch.bfloat16, device=dev)
-    launches_per_step = 2 if world == 1 else 3
+    launches_per_step = 5 if vsa_topk else (2 if world == 1 else 3)
     attn_events = []
 
     def step(p, record=False):
+        if vsa_topk:
+            if record:
+                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+            o = vsa.vsa_attention(p[0], p[1], p[2], p[3], vctx)
+            if record:
+                e1.record()
+                attn_events.append((e0, e1))
+            return o
         q, k, v = wan.qk_prep(p, wq, wk, cos, sin, heads)
         q, k, v = q.view(bh, length, 128), k.view(bh, length, 128), v.view(bh, length, 128)
         if record:
@@ -315,7 +348,8 @@ def main():
                 ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
                 config=cfg, per_gpu_tflops=value / world, frac_of_bf16_peak_burst=value / world / pk["burst"],
                 frac_of_bf16_peak_sustained=value / world / pk["sustained"], peaks=pk,
-                roofline=dict(bound="tensor", kernel="fv_sdpa_fwd_d128", achieved=achieved, peak=pk["sustained"], unit="TFLOP/s",
+                roofline=dict(bound="tensor", kernel="fv_vsa_fine_kernel (+4 small kernels in the timed span)" if vsa_topk else "fv_sdpa_fwd_d128",
+                              achieved=achieved, peak=pk["sustained"], unit="TFLOP/s",
                               frac=achieved / pk["sustained"], frac_of_burst=achieved / pk["burst"], of=pk["source"],
                               ms_per_launch_set=attn_ms, traffic=traffic,
                               note="attention launch(es) of one step timed with CUDA events inside the timed region; "

@@ -10,30 +10,32 @@ constexpr int kStages = 4;
 
 // One entry per softmax variant (see sdpa_body); FV_SDPA_VARIANT picks one at run time for A/B timing,
 // kDefaultVariant otherwise.
-template <int VAR>
+template <int VAR, bool MASKED>
 __global__ void __launch_bounds__(kThreads, 1)
 fv_sdpa_fwd_d128(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                  const __grid_constant__ CUtensorMap tv, const __grid_constant__ Params p) {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL)
     extern __shared__ __align__(1024) unsigned char fv_smem[];
-    sdpa_body<kStages, VAR>(&tq, &tk, &tv, p, fv_smem);
+    sdpa_body<kStages, VAR, MASKED>(&tq, &tk, &tv, p, fv_smem);
 #endif
 }
 
 constexpr int kDefaultVariant = 0;
 typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const Params);
-static KernelFn kernel_for(int var) {
+static KernelFn kernel_for(int var, bool masked) {
     switch (var) {
-        case 1: return fv_sdpa_fwd_d128<1>;
-        case 3: return fv_sdpa_fwd_d128<3>;
-        case 5: return fv_sdpa_fwd_d128<5>;
-        case 8: return fv_sdpa_fwd_d128<8>;
-        case 9: return fv_sdpa_fwd_d128<9>;
-        case 11: return fv_sdpa_fwd_d128<11>;
-        case 13: return fv_sdpa_fwd_d128<13>;
-        case 2: return fv_sdpa_fwd_d128<2>;
-        case 10: return fv_sdpa_fwd_d128<10>;
-        default: return fv_sdpa_fwd_d128<0>;
+        case 1: return masked ? fv_sdpa_fwd_d128<1, true> : fv_sdpa_fwd_d128<1, false>;
+        case 3: return masked ? fv_sdpa_fwd_d128<3, true> : fv_sdpa_fwd_d128<3, false>;
+        case 5: return masked ? fv_sdpa_fwd_d128<5, true> : fv_sdpa_fwd_d128<5, false>;
+        case 8: return masked ? fv_sdpa_fwd_d128<8, true> : fv_sdpa_fwd_d128<8, false>;
+        case 9: return masked ? fv_sdpa_fwd_d128<9, true> : fv_sdpa_fwd_d128<9, false>;
+        case 11: return masked ? fv_sdpa_fwd_d128<11, true> : fv_sdpa_fwd_d128<11, false>;
+        case 13: return masked ? fv_sdpa_fwd_d128<13, true> : fv_sdpa_fwd_d128<13, false>;
+        case 2: return masked ? fv_sdpa_fwd_d128<2, true> : fv_sdpa_fwd_d128<2, false>;
+        case 16: return masked ? fv_sdpa_fwd_d128<16, true> : fv_sdpa_fwd_d128<16, false>;
+        case 24: return masked ? fv_sdpa_fwd_d128<24, true> : fv_sdpa_fwd_d128<24, false>;
+        case 10: return masked ? fv_sdpa_fwd_d128<10, true> : fv_sdpa_fwd_d128<10, false>;
+        default: return masked ? fv_sdpa_fwd_d128<0, true> : fv_sdpa_fwd_d128<0, false>;
     }
 }
 static int chosen_variant() {
@@ -41,7 +43,7 @@ static int chosen_variant() {
     if (v < 0) {
         const char* e = getenv("FV_SDPA_VARIANT");
         v = e ? atoi(e) : kDefaultVariant;
-        if (v < 0 || v > 15) v = kDefaultVariant;
+        if (v < 0 || v > 31) v = kDefaultVariant;
     }
     return v;
 }
@@ -118,13 +120,14 @@ static int launch(cudaStream_t stream, const void* q, const void* k, const void*
         if (rc != FV_RAN) return rc;
     }
 
-    static bool attr_set[64][16] = {};
+    static bool attr_set[64][32][2] = {};
     constexpr uint32_t smem = smem_bytes<kStages>();
     const int var = chosen_variant();
-    const KernelFn fn = kernel_for(var);
-    if (!attr_set[dev][var]) {
+    const bool masked = mask_mode != FV_MASK_NONE;
+    const KernelFn fn = kernel_for(var, masked);
+    if (!attr_set[dev][var][masked]) {
         FV_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set[dev][var] = true;
+        attr_set[dev][var][masked] = true;
     }
     fn<<<(unsigned)grid, kThreads, smem, stream>>>(tq, tk, tv, p);
     FV_CUDA(cudaGetLastError());

@@ -70,7 +70,7 @@ FV_DEV int sat_mul(int a, int b) {
 
 // The key tiles a CTA visits, identical in every role.  f(seg, t, k0, lim):
 // segment, tile index inside it, global index of column 0, valid columns.
-template <class F>
+template <bool MASKED, class F>
 FV_DEV void walk_tiles(const Params& p, int vis_lo, int vis_hi, int vis_sink, F&& f) {
     for (int seg = 0; seg < p.nseg; seg++) {
         const int len = p.seg_len[seg], start = p.seg_start[seg];
@@ -78,7 +78,7 @@ FV_DEV void walk_tiles(const Params& p, int vis_lo, int vis_hi, int vis_sink, F&
         for (int t = 0; t < nt; t++) {
             const int k0 = start + t * kBN;
             const int lim = min(kBN, len - t * kBN);
-            if (p.mask_mode) {
+            if constexpr (MASKED) {
                 const int k1 = k0 + lim;
                 if (!((k0 < vis_hi && k1 > vis_lo) || k0 < vis_sink)) continue;
             }
@@ -110,11 +110,41 @@ FV_DEV void issue_pv(uint32_t tO, uint32_t tP, uint32_t sV, bool acc) {
 FV_DEV float u2f(uint32_t u) { return __uint_as_float(u); }
 FV_DEV uint32_t f2u(float f) { return __float_as_uint(f); }
 
+// Row maximum of the 128 scores (V3: three-input max).
+template <bool V3>
+FV_DEV float row_max(const uint32_t (&u)[128]) {
+    using namespace fvp;
+    if constexpr (V3) {
+        float x0 = max3(u2f(u[0]), u2f(u[1]), u2f(u[2])), x1 = max3(u2f(u[3]), u2f(u[4]), u2f(u[5]));
+        float x2 = max3(u2f(u[6]), u2f(u[7]), u2f(u[8])), x3 = max3(u2f(u[9]), u2f(u[10]), u2f(u[11]));
+#pragma unroll
+        for (int c = 12; c < 124; c += 8) {
+            x0 = max3(x0, u2f(u[c]), u2f(u[c + 1]));
+            x1 = max3(x1, u2f(u[c + 2]), u2f(u[c + 3]));
+            x2 = max3(x2, u2f(u[c + 4]), u2f(u[c + 5]));
+            x3 = max3(x3, u2f(u[c + 6]), u2f(u[c + 7]));
+        }
+        x0 = max3(x0, u2f(u[124]), u2f(u[125]));
+        x1 = max3(x1, u2f(u[126]), u2f(u[127]));
+        return fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
+    } else {
+        float x0 = u2f(u[0]), x1 = u2f(u[1]), x2 = u2f(u[2]), x3 = u2f(u[3]);
+#pragma unroll
+        for (int c = 4; c < 128; c += 4) {
+            x0 = fmaxf(x0, u2f(u[c]));
+            x1 = fmaxf(x1, u2f(u[c + 1]));
+            x2 = fmaxf(x2, u2f(u[c + 2]));
+            x3 = fmaxf(x3, u2f(u[c + 3]));
+        }
+        return fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
+    }
+}
+
 // P = 2^(s*sl2 + noff) for the 128 scores of one row: bf16 pairs stored to TMEM at tP, returns the f32 row sum.
 // PACK: two-wide FMA / ADD.  PMASK >= 0: the pairs w of each half with (w & PMASK) == PMASK go through the
 // FMA-pipe exponential (1 -> every second pair, 3 -> every fourth), the others through MUFU ex2.
 template <bool PACK, int PMASK>
-FV_DEV float exp_and_store(uint32_t (&u)[128], float sl2, float noff, uint32_t tP) {
+FV_DEV float exp_and_store(const uint32_t (&u)[128], float sl2, float noff, uint32_t tP) {
     using namespace fvp;
     float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
     uint64_t ya = pack_f32x2(0.f, 0.f), yb = pack_f32x2(0.f, 0.f);
@@ -163,8 +193,9 @@ FV_DEV float exp_and_store(uint32_t (&u)[128], float sl2, float noff, uint32_t t
 
 // VAR bits: 1 = packed f32x2 scale-and-subtract and row sum; 2 = half of the exponentials of an unmasked
 // tile on the FMA pipe (pairs 1, 3, 5, ... of each group of four columns); 4 = a quarter of them instead;
-// 8 = three-input max.
-template <int NS, int VAR>
+// 8 = three-input max; 16 = exponentials against the current reference before the row maximum is known.
+// MASKED = false compiles the block-causal bookkeeping out (dense calls: fewer live registers in the softmax loop).
+template <int NS, int VAR, bool MASKED>
 FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtensorMap* tv, const Params& p,
                       unsigned char* smem_raw) {
     using namespace fvp;
@@ -219,7 +250,7 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
     // Keys any row of this CTA may see (block-causal): [vis_lo, vis_hi) U [0, vis_sink).
     int vis_lo = 0, vis_hi = 0x7fffffff, vis_sink = 0;
     const int bt = max(p.block_tokens, 1);
-    if (p.mask_mode) {
+    if constexpr (MASKED) {
         const int qg_min = p.q_row0 + q0;
         const int qg_max = p.q_row0 + min(q0 + kRowsPerCta - 1, p.sq - 1);
         const int tq_min = qg_min / bt, tq_max = qg_max / bt;
@@ -241,7 +272,7 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
         const int qr = q0 + 128 * tile + row;
         // Keys this row may see: [r_lo, r_hi) U [0, r_sink).
         int r_lo = 0, r_hi = 0x7fffffff, r_sink = 0;
-        if (p.mask_mode) {
+        if constexpr (MASKED) {
             const int tqr = (p.q_row0 + qr) / bt;
             r_hi = sat_mul(tqr + 1, bt);
             r_lo = p.window > 0 ? sat_mul(max(0, tqr - p.window + 1), bt) : 0;
@@ -251,7 +282,7 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
         float m = NEG, l = 0.f;
         int it = 0;
         bool ok = true;
-        walk_tiles(p, vis_lo, vis_hi, vis_sink, [&](int, int, int k0, int lim) -> bool {
+        walk_tiles<MASKED>(p, vis_lo, vis_hi, vis_sink, [&](int, int, int k0, int lim) -> bool {
             // Warp-uniform outcome: the TMEM instructions below are warp-collective.
             if (!__all_sync(0xffffffffu, mbar_wait(b_s + 8 * tile, it & 1, ctl))) { ok = false; return false; }
             tc_fence_after();
@@ -263,42 +294,43 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
             tmem_ld_wait();
             tmem_pin(u);
             // Visible columns of this row in this tile: [c_lo, c_hi) U [0, c_sink).
-            const int c_lo = min(max(r_lo - k0, 0), lim);
-            const int c_hi = min(max(r_hi - k0, 0), lim);
-            const int c_sink = min(max(r_sink - k0, 0), lim);
-            const bool full_tile = (c_lo == 0 && c_hi == kBN) || c_sink == kBN;
-            if (!full_tile) {
+            bool full_tile;
+            if constexpr (MASKED) {
+                const int c_lo = min(max(r_lo - k0, 0), lim);
+                const int c_hi = min(max(r_hi - k0, 0), lim);
+                const int c_sink = min(max(r_sink - k0, 0), lim);
+                full_tile = (c_lo == 0 && c_hi == kBN) || c_sink == kBN;
+                if (!full_tile) {
 #pragma unroll
-                for (int c = 0; c < 128; c++) {
-                    const bool vis = (c >= c_lo && c < c_hi) || c < c_sink;
-                    u[c] = vis ? u[c] : f2u(NEG);
+                    for (int c = 0; c < 128; c++) {
+                        const bool vis = (c >= c_lo && c < c_hi) || c < c_sink;
+                        u[c] = vis ? u[c] : f2u(NEG);
+                    }
                 }
-            }
-            float tmax;
-            if constexpr ((VAR & 8) != 0) {
-                float x0 = max3(u2f(u[0]), u2f(u[1]), u2f(u[2])), x1 = max3(u2f(u[3]), u2f(u[4]), u2f(u[5]));
-                float x2 = max3(u2f(u[6]), u2f(u[7]), u2f(u[8])), x3 = max3(u2f(u[9]), u2f(u[10]), u2f(u[11]));
-#pragma unroll
-                for (int c = 12; c < 124; c += 8) {
-                    x0 = max3(x0, u2f(u[c]), u2f(u[c + 1]));
-                    x1 = max3(x1, u2f(u[c + 2]), u2f(u[c + 3]));
-                    x2 = max3(x2, u2f(u[c + 4]), u2f(u[c + 5]));
-                    x3 = max3(x3, u2f(u[c + 6]), u2f(u[c + 7]));
-                }
-                x0 = max3(x0, u2f(u[124]), u2f(u[125]));
-                x1 = max3(x1, u2f(u[126]), u2f(u[127]));
-                tmax = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
             } else {
-                float x0 = u2f(u[0]), x1 = u2f(u[1]), x2 = u2f(u[2]), x3 = u2f(u[3]);
+                (void)k0;
+                full_tile = lim == kBN;  // only a segment's last tile can be short
+                if (!full_tile) {
 #pragma unroll
-                for (int c = 4; c < 128; c += 4) {
-                    x0 = fmaxf(x0, u2f(u[c]));
-                    x1 = fmaxf(x1, u2f(u[c + 1]));
-                    x2 = fmaxf(x2, u2f(u[c + 2]));
-                    x3 = fmaxf(x3, u2f(u[c + 3]));
+                    for (int c = 0; c < 128; c++) u[c] = c < lim ? u[c] : f2u(NEG);
                 }
-                tmax = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
             }
+            bool settled = false;  // warp-uniform: the speculative pass below already produced this tile's P
+            if constexpr ((VAR & 16) != 0) {
+                // Every row of the warp already has a finite reference: exponentiate against it right away and
+                // compute the row maximum beside it (independent instruction streams; the maximum only decides
+                // whether the reference has to move, which is rare after the first tiles).
+                if (__all_sync(0xffffffffu, m != NEG)) {
+                    const float rs = exp_and_store<(VAR & 1) != 0, -1>(u, sl2, -m, tP);
+                    const float t2 = row_max<(VAR & 8) != 0>(u) * sl2;
+                    if (!__any_sync(0xffffffffu, t2 > m + kLazyLog2)) {
+                        l += rs;
+                        settled = true;
+                    }
+                }
+            }
+            if (!settled) {
+            const float tmax = row_max<(VAR & 8) != 0>(u);
             const float tm2 = tmax * sl2;
             const bool grow = tm2 > m + kLazyLog2;
             float a = 1.f;
@@ -330,6 +362,7 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
                 rowsum = exp_and_store<(VAR & 1) != 0, kPolyMask>(u, sl2, noff, tP);
             else rowsum = exp_and_store<(VAR & 1) != 0, -1>(u, sl2, noff, tP);
             l = fmaf(l, a, rowsum);
+            }
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(b_p + 8 * tile);
@@ -424,7 +457,7 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
             tma_load4(sQ + kTileB + kPanelB, tq, b_q, 64, q0 + 128, bh, 0);
             int idx = 0;
             bool ok = true;
-            walk_tiles(p, vis_lo, vis_hi, vis_sink, [&](int seg, int t, int, int) -> bool {
+            walk_tiles<MASKED>(p, vis_lo, vis_hi, vis_sink, [&](int seg, int t, int, int) -> bool {
 #pragma unroll 1
                 for (int half = 0; half < 2; half++) {
                     const int slot = idx % NS, use = idx / NS;
@@ -455,7 +488,7 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
             WaitCtl ctl{abort_ptr, p.status, 2};
             // This role needs only the number of visited tiles, not which ones.
             int nvis = 0;
-            walk_tiles(p, vis_lo, vis_hi, vis_sink, [&](int, int, int, int) -> bool { nvis++; return true; });
+            walk_tiles<MASKED>(p, vis_lo, vis_hi, vis_sink, [&](int, int, int, int) -> bool { nvis++; return true; });
             bool ok = mbar_wait(b_q, 0, ctl);
             tc_fence_after();
             int it = 0;
