@@ -1,5 +1,6 @@
 // Entry kernels and host launcher of the head-dim-128 SDPA forward.
 #include "sdpa_fwd.cuh"
+#include "sdpa_fwd64.cuh"
 #include "fv_runtime.h"
 #include <math.h>
 #include <stdlib.h>
@@ -20,10 +21,23 @@ fv_sdpa_fwd_d128(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 #endif
 }
 
+// The double-buffered-S schedule (sdpa_fwd64.cuh); variants 100 + VAR.
+template <int VAR, bool MASKED>
+__global__ void __launch_bounds__(kThreads, 1)
+fv_sdpa_fwd64_d128(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                   const __grid_constant__ CUtensorMap tv, const __grid_constant__ Params p) {
+#if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL)
+    extern __shared__ __align__(1024) unsigned char fv_smem[];
+    sdpa_body64<kStages, VAR, MASKED>(&tq, &tk, &tv, p, fv_smem);
+#endif
+}
+
 constexpr int kDefaultVariant = 0;
 typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const Params);
 static KernelFn kernel_for(int var, bool masked) {
     switch (var) {
+        case 100: return masked ? fv_sdpa_fwd64_d128<0, true> : fv_sdpa_fwd64_d128<0, false>;
+        case 101: return masked ? fv_sdpa_fwd64_d128<1, true> : fv_sdpa_fwd64_d128<1, false>;
         case 1: return masked ? fv_sdpa_fwd_d128<1, true> : fv_sdpa_fwd_d128<1, false>;
         case 3: return masked ? fv_sdpa_fwd_d128<3, true> : fv_sdpa_fwd_d128<3, false>;
         case 5: return masked ? fv_sdpa_fwd_d128<5, true> : fv_sdpa_fwd_d128<5, false>;
@@ -32,6 +46,17 @@ static KernelFn kernel_for(int var, bool masked) {
         case 11: return masked ? fv_sdpa_fwd_d128<11, true> : fv_sdpa_fwd_d128<11, false>;
         case 13: return masked ? fv_sdpa_fwd_d128<13, true> : fv_sdpa_fwd_d128<13, false>;
         case 2: return masked ? fv_sdpa_fwd_d128<2, true> : fv_sdpa_fwd_d128<2, false>;
+        case 64: return masked ? fv_sdpa_fwd_d128<64, true> : fv_sdpa_fwd_d128<64, false>;
+        case 128: return masked ? fv_sdpa_fwd_d128<128, true> : fv_sdpa_fwd_d128<128, false>;
+        case 256: return masked ? fv_sdpa_fwd_d128<256, true> : fv_sdpa_fwd_d128<256, false>;
+        case 448: return masked ? fv_sdpa_fwd_d128<448, true> : fv_sdpa_fwd_d128<448, false>;
+        case 960: return masked ? fv_sdpa_fwd_d128<960, true> : fv_sdpa_fwd_d128<960, false>;
+        case 1472: return masked ? fv_sdpa_fwd_d128<1472, true> : fv_sdpa_fwd_d128<1472, false>;
+        case 1984: return masked ? fv_sdpa_fwd_d128<1984, true> : fv_sdpa_fwd_d128<1984, false>;
+        case 4032: return masked ? fv_sdpa_fwd_d128<4032, true> : fv_sdpa_fwd_d128<4032, false>;
+        case 6080: return masked ? fv_sdpa_fwd_d128<6080, true> : fv_sdpa_fwd_d128<6080, false>;
+        case 10176: return masked ? fv_sdpa_fwd_d128<10176, true> : fv_sdpa_fwd_d128<10176, false>;
+        case 32: return masked ? fv_sdpa_fwd_d128<32, true> : fv_sdpa_fwd_d128<32, false>;
         case 16: return masked ? fv_sdpa_fwd_d128<16, true> : fv_sdpa_fwd_d128<16, false>;
         case 24: return masked ? fv_sdpa_fwd_d128<24, true> : fv_sdpa_fwd_d128<24, false>;
         case 10: return masked ? fv_sdpa_fwd_d128<10, true> : fv_sdpa_fwd_d128<10, false>;
@@ -43,7 +68,7 @@ static int chosen_variant() {
     if (v < 0) {
         const char* e = getenv("FV_SDPA_VARIANT");
         v = e ? atoi(e) : kDefaultVariant;
-        if (v < 0 || v > 31) v = kDefaultVariant;
+        if (v < 0 || v > 16383) v = kDefaultVariant;
     }
     return v;
 }
@@ -120,14 +145,14 @@ static int launch(cudaStream_t stream, const void* q, const void* k, const void*
         if (rc != FV_RAN) return rc;
     }
 
-    static bool attr_set[64][32][2] = {};
+    static bool attr_set[8][16384][2] = {};
     constexpr uint32_t smem = smem_bytes<kStages>();
     const int var = chosen_variant();
     const bool masked = mask_mode != FV_MASK_NONE;
     const KernelFn fn = kernel_for(var, masked);
-    if (!attr_set[dev][var][masked]) {
+    if (!attr_set[dev & 7][var][masked]) {
         FV_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set[dev][var][masked] = true;
+        attr_set[dev & 7][var][masked] = true;
     }
     fn<<<(unsigned)grid, kThreads, smem, stream>>>(tq, tk, tv, p);
     FV_CUDA(cudaGetLastError());

@@ -46,6 +46,22 @@ struct Rng {
     }
 };
 
+// N(0,1) rounded to bf16.  Large tensors draw from a table of 2^20 normals through a hashed index (a full
+// Box-Muller stream for a billion elements would take minutes on one host thread).
+static void fill_normal(std::vector<uint16_t>& x, Rng& r) {
+    if (x.size() <= (1u << 22)) {
+        for (auto& e : x) e = f2bf(r.normal());
+        return;
+    }
+    std::vector<uint16_t> table(1u << 20);
+    for (auto& e : table) e = f2bf(r.normal());
+    uint64_t s = r.next() | 1ull;
+    for (size_t i = 0; i < x.size(); i++) {
+        s = s * 6364136223846793005ull + 1442695040888963407ull;
+        x[i] = table[(s >> 40) & ((1u << 20) - 1)];
+    }
+}
+
 struct Case {
     int bh, sq, sk, bt, win, sink;
 };
@@ -69,9 +85,9 @@ static int run_case(const Case& c, bool bench, int out_bf16) {
     const size_t nq = (size_t)c.bh * c.sq * 128, nk = (size_t)c.bh * c.sk * 128;
     std::vector<uint16_t> q(nq), k(nk), v(nk);
     Rng r(1000003ull * c.bh + 7919ull * c.sq + c.sk);
-    for (auto& x : q) x = f2bf(r.normal());
-    for (auto& x : k) x = f2bf(r.normal());
-    for (auto& x : v) x = f2bf(r.normal());
+    fill_normal(q, r);
+    fill_normal(k, r);
+    fill_normal(v, r);
     void *dq, *dk, *dv, *dout;
     const size_t out_bytes = nq * (out_bf16 ? 2 : 4);
     CK(cudaMalloc(&dq, nq * 2));
