@@ -32,7 +32,9 @@ fv_sdpa_fwd64_d128(const __grid_constant__ CUtensorMap tq, const __grid_constant
 #endif
 }
 
-constexpr int kDefaultVariant = 0;
+// 13 = packed f32x2 arithmetic + a quarter of the exponentials of unmasked tiles on the FMA pipe + three-input
+// max: the fastest of the measured mixes (profiles/fv_sdpa_variants.md).
+constexpr int kDefaultVariant = 13;
 typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const Params);
 static KernelFn kernel_for(int var, bool masked) {
     switch (var) {
@@ -56,6 +58,9 @@ static KernelFn kernel_for(int var, bool masked) {
         case 4032: return masked ? fv_sdpa_fwd_d128<4032, true> : fv_sdpa_fwd_d128<4032, false>;
         case 6080: return masked ? fv_sdpa_fwd_d128<6080, true> : fv_sdpa_fwd_d128<6080, false>;
         case 10176: return masked ? fv_sdpa_fwd_d128<10176, true> : fv_sdpa_fwd_d128<10176, false>;
+        case 4: return masked ? fv_sdpa_fwd_d128<4, true> : fv_sdpa_fwd_d128<4, false>;
+        case 12: return masked ? fv_sdpa_fwd_d128<12, true> : fv_sdpa_fwd_d128<12, false>;
+        case 7: return masked ? fv_sdpa_fwd_d128<7, true> : fv_sdpa_fwd_d128<7, false>;
         case 32: return masked ? fv_sdpa_fwd_d128<32, true> : fv_sdpa_fwd_d128<32, false>;
         case 16: return masked ? fv_sdpa_fwd_d128<16, true> : fv_sdpa_fwd_d128<16, false>;
         case 24: return masked ? fv_sdpa_fwd_d128<24, true> : fv_sdpa_fwd_d128<24, false>;

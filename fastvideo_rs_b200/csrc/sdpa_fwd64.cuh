@@ -64,19 +64,36 @@ struct HalfCursor {
 // S half (TMEM 128 x 64 f32) = Q (128 x 128) . K^T (64 keys: rows 64*hh.. of the K tile)
 FV_DEV void issue_qk_half(uint32_t tS, uint32_t sQ, uint32_t sK, int hh) {
     constexpr uint32_t idesc = fvp::umma_idesc_bf16(128, 64, 0);
-#pragma unroll
-    for (int kk = 0; kk < 8; kk++) {
-        const uint32_t off = (uint32_t)(kk >> 2) * kPanelB + (uint32_t)(kk & 3) * 32u;
-        fvp::umma_ss(tS, fvp::umma_desc_sw128(sQ + off, 16, 1024), fvp::umma_desc_sw128(sK + off + (uint32_t)hh * 8192u, 16, 1024),
-                     idesc, kk > 0);
-    }
+    const uint64_t a0 = fvp::umma_desc_sw128(sQ, 16, 1024), b0 = fvp::umma_desc_sw128(sK + (uint32_t)hh * 8192u, 16, 1024);
+    asm volatile(
+        "{\n\t.reg .pred pt, pf;\n\t.reg .b64 a, b;\n\t"
+        "setp.ne.b32 pf, %3, %3;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+        "add.s64 a, %1, 2;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 4;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 6;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 1024;\n\tadd.s64 b, %2, 1024;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 1026;\n\tadd.s64 b, %2, 1026;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 1028;\n\tadd.s64 b, %2, 1028;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 1030;\n\tadd.s64 b, %2, 1030;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "}"
+        ::"r"(tS), "l"(a0), "l"(b0), "r"(idesc)
+        : "memory");
 }
 // O (TMEM 128 x 128 f32) (+)= P (TMEM bf16 128 x 64 keys) . V (keys 64*hh.. of the V tile, 64 x 128, MN-major)
 FV_DEV void issue_pv_half(uint32_t tO, uint32_t tP, uint32_t sV, int hh, bool acc) {
     constexpr uint32_t idesc = fvp::umma_idesc_bf16(128, 128, 1);
-#pragma unroll
-    for (int kk = 0; kk < 4; kk++)
-        fvp::umma_ts(tO, tP + 8u * kk, fvp::umma_desc_sw128(sV + 2048u * (uint32_t)(4 * hh + kk), kPanelB, 1024), idesc, acc || kk > 0);
+    const uint64_t b0 = fvp::umma_desc_sw128(sV + 8192u * (uint32_t)hh, kPanelB, 1024);
+    asm volatile(
+        "{\n\t.reg .pred pt, p0;\n\t.reg .b64 b;\n\t.reg .b32 t;\n\t"
+        "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+        "add.u32 t, %1, 8;\n\tadd.s64 b, %2, 128;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
+        "add.u32 t, %1, 16;\n\tadd.s64 b, %2, 256;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
+        "add.u32 t, %1, 24;\n\tadd.s64 b, %2, 384;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
+        "}"
+        ::"r"(tO), "r"(tP), "l"(b0), "r"(idesc), "r"((uint32_t)acc)
+        : "memory");
 }
 
 // VAR bits: 1 = P against the current reference before the half's maximum is known (in registers; stored only if

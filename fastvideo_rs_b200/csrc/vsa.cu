@@ -489,21 +489,41 @@ fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
             if (!mbar_wait(b_full + 8 * slotK, (ik / kFineNS) & 1, ctl)) { ok = false; break; }
             tc_fence_after();
             const uint32_t sK = ring + slotK * kKvTileB, sV = ring + slotV * kKvTileB;
-#pragma unroll
-            for (int kk = 0; kk < 8; kk++) {
-                const uint32_t qo = (uint32_t)(kk >> 2) * kQPanelB + (uint32_t)(kk & 3) * 32u;
-                const uint32_t ko = (uint32_t)(kk >> 2) * kKvPanelB + (uint32_t)(kk & 3) * 32u;
-                umma_ss(tbase, umma_desc_sw128(sQ + qo, 16, 1024), umma_desc_sw128(sK + ko, 16, 1024), idesc_qk, kk > 0);
+            {
+                const uint64_t a0 = umma_desc_sw128(sQ, 16, 1024), b0 = umma_desc_sw128(sK, 16, 1024);
+                asm volatile(
+                    "{\n\t.reg .pred pt, pf;\n\t.reg .b64 a, b;\n\t"
+                    "setp.ne.b32 pf, %3, %3;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
+                    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+                    "add.s64 a, %1, 2;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                    "add.s64 a, %1, 4;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                    "add.s64 a, %1, 6;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                    "add.s64 a, %1, 1024;\n\tadd.s64 b, %2, 512;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                    "add.s64 a, %1, 1026;\n\tadd.s64 b, %2, 514;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                    "add.s64 a, %1, 1028;\n\tadd.s64 b, %2, 516;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                    "add.s64 a, %1, 1030;\n\tadd.s64 b, %2, 518;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                    "}"
+                    ::"r"(tbase), "l"(a0), "l"(b0), "r"(idesc_qk)
+                    : "memory");
             }
             umma_commit(b_s);
             umma_commit(b_empty + 8 * slotK);
             if (!mbar_wait(b_full + 8 * slotV, (iv / kFineNS) & 1, ctl)) { ok = false; break; }
             if (!mbar_wait(b_p, j & 1, ctl)) { ok = false; break; }
             tc_fence_after();
-#pragma unroll
-            for (int kk = 0; kk < 4; kk++)
-                umma_ts(tbase + 128u, tbase + 8u * kk, umma_desc_sw128(sV + 2048u * kk, kKvPanelB, 1024), idesc_pv,
-                        j > 0 || kk > 0);
+            {
+                const uint64_t b0 = umma_desc_sw128(sV, kKvPanelB, 1024);
+                asm volatile(
+                    "{\n\t.reg .pred pt, p0;\n\t.reg .b64 b;\n\t.reg .b32 t;\n\t"
+                    "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
+                    "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+                    "add.u32 t, %1, 8;\n\tadd.s64 b, %2, 128;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
+                    "add.u32 t, %1, 16;\n\tadd.s64 b, %2, 256;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
+                    "add.u32 t, %1, 24;\n\tadd.s64 b, %2, 384;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
+                    "}"
+                    ::"r"(tbase + 128u), "r"(tbase), "l"(b0), "r"(idesc_pv), "r"((uint32_t)(j > 0))
+                    : "memory");
+            }
             umma_commit(b_empty + 8 * slotV);
             if (j == nent - 1) umma_commit(b_o);
         }
