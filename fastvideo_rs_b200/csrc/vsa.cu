@@ -112,9 +112,12 @@ __global__ void __launch_bounds__(128) vsa_coarse_kernel(const float* __restrict
     if (lane == 0) redd[warp] = z;
     __syncthreads();
     z = (redd[0] + redd[1]) + (redd[2] + redd[3]);
+    for (int i = t; i < nt; i += 128) wexp[i] = wexp[i] / z;  // the weights, once (same f64 division as the host)
+    __syncthreads();
     float acc = 0.f;
     const float* vch = vc + (size_t)bh * nt * kD + t;
-    for (int kt = 0; kt < nt; kt++) acc = __fadd_rn(acc, (float)((wexp[kt] / z) * (double)vch[(size_t)kt * kD]));
+#pragma unroll 8
+    for (int kt = 0; kt < nt; kt++) acc = __fadd_rn(acc, (float)(wexp[kt] * (double)vch[(size_t)kt * kD]));
     coarse[((size_t)bh * nt + qt) * kD + t] = acc;
 }
 
@@ -191,9 +194,9 @@ __global__ void __launch_bounds__(256) vsa_topk_kernel(const float* __restrict__
 // rows 0-63 are tile 2p, rows 64-127 tile 2p+1), 4 list builder + TMA producer, 5 MMA issuer.
 // The CTA walks the ascending union of the two tiles' selections, one 64-key tile per step; an
 // entry word says which of the two query tiles selected it (the other one's rows get P = 0) and how
-// many of its 64 slots are real keys.  TMEM (256 columns, two CTAs per SM): S at 0 (64 columns; the
-// bf16 P overwrites columns 0-31), O at 128 (128 columns).  One S buffer: the steps of one CTA are
-// serial and the second CTA of the SM fills the gaps.
+// many of its 64 slots are real keys.  TMEM (256 columns, two CTAs per SM): two S buffers at 0 and 64 (64
+// columns each; the bf16 P of a step overwrites columns 0-31 of its buffer), O at 128 (128 columns).  Q.K^T runs two
+// steps ahead of P.V, so the softmax of step j+1 starts as soon as that of step j ends.
 constexpr int kFineThreads = 192;
 constexpr int kFineNS = 4;
 constexpr uint32_t kKvTileB = 16384;   // 64 x 128 bf16: two 8 KB panels
@@ -233,9 +236,10 @@ fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     const uint32_t b_q = bars;
     const uint32_t b_full = b_q + 8;
     const uint32_t b_empty = b_full + 8 * kFineNS;
-    const uint32_t b_s = b_empty + 8 * kFineNS;
-    const uint32_t b_p = b_s + 8;
-    const uint32_t b_o = b_p + 8;
+    const uint32_t b_s = b_empty + 8 * kFineNS;  // [2]: S buffer ready
+    const uint32_t b_p = b_s + 16;               // [2]: P stored in that buffer
+    const uint32_t b_od = b_p + 16;              // one phase per P.V
+    const uint32_t b_o = b_od + 8;               // the last P.V
     const uint32_t b_drain = b_o + 8;
     const uint32_t tslot = b_drain + 8;
     const uint32_t aflag = tslot + 4;
@@ -258,8 +262,11 @@ fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
             mbar_init(b_full + 8 * i, 1);
             mbar_init(b_empty + 8 * i, 1);
         }
-        mbar_init(b_s, 1);
-        mbar_init(b_p, 128);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(b_s + 8 * i, 1);
+            mbar_init(b_p + 8 * i, 128);
+        }
+        mbar_init(b_od, 1);
         mbar_init(b_o, 1);
         mbar_init(b_drain, 1);
         *abort_ptr = (*(volatile int*)p.status != FV_ST_OK) ? 1 : 0;
@@ -316,7 +323,7 @@ fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         WaitCtl ctl{abort_ptr, p.status, 13};
         const int row = warp * 32 + lane, half = row >> 6;
         const uint32_t tl = tbase + ((uint32_t)(warp * 32) << 16);
-        const uint32_t tS = tl, tP = tl, tO = tl + 128u;
+        const uint32_t tO = tl + 128u;
         const float sl2 = p.sl2;
         float m = NEG, l = 0.f;
         bool ok = true;
@@ -325,7 +332,9 @@ fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
             const uint32_t e = list[j];
             const int valid = (int)((e >> 20) & 127u);
             const bool vis = ((e >> (27 + half)) & 1u) != 0u;  // warp-uniform: a warp lies inside one half
-            if (!__all_sync(0xffffffffu, mbar_wait(b_s, j & 1, ctl))) { ok = false; break; }
+            const int bsel = j & 1;
+            const uint32_t tS = tl + 64u * bsel, tP = tS;
+            if (!__all_sync(0xffffffffu, mbar_wait(b_s + 8 * bsel, (j >> 1) & 1, ctl))) { ok = false; break; }
             tc_fence_after();
             uint32_t pw[32];
             if (vis) {
@@ -356,8 +365,10 @@ fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
                     m = tm2;
                 }
                 const float off = (m == NEG) ? 0.f : m;
-                // S_j done implies PV_{j-1} done (same issuing thread, in order): O is quiet
+                // S_j done only implies PV_{j-2} done (Q.K^T runs two steps ahead): wait for PV_{j-1} before touching O
                 if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(b_od, (j - 1) & 1, ctl))) { ok = false; break; }
+                    tc_fence_after();
 #pragma unroll 1
                     for (int q = 0; q < 4; q++) {
                         uint32_t o[32];
@@ -386,7 +397,7 @@ fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
             tmem_st32(tP, pw);
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(b_p);
+            mbar_arrive(b_p + 8 * bsel);
         }
         if (ok && nent > 0) ok = __all_sync(0xffffffffu, mbar_wait(b_o, 0, ctl));
         tc_fence_after();
@@ -452,20 +463,25 @@ fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
             tma_prefetch_desc(&tv);
             int idx = 0;
             bool ok = true;
+            // Ring order = consumption order: K0 K1 V0 K2 V1 K3 ... (Q.K^T runs two steps ahead of P.V)
+            auto load = [&](int j, bool is_v) {
+                if (!ok) return;
+                const int tile = (int)(list[j] & 0xFFFFFu);
+                const int slot = idx % kFineNS, use = idx / kFineNS;
+                if (use > 0 && !mbar_wait(b_empty + 8 * slot, (use - 1) & 1, ctl)) { ok = false; return; }
+                const uint32_t dst = ring + slot * kKvTileB, bar = b_full + 8 * slot;
+                const CUtensorMap* map = is_v ? &tv : &tk;
+                mbar_expect_tx(bar, kKvTileB);
+                tma_load4(dst, map, bar, 0, tile * TE, bh, 0);
+                tma_load4(dst + kKvPanelB, map, bar, 64, tile * TE, bh, 0);
+                idx++;
+            };
+            if (nent > 0) load(0, false);
+            if (nent > 1) load(1, false);
 #pragma unroll 1
             for (int j = 0; j < nent && ok; j++) {
-                const int tile = (int)(list[j] & 0xFFFFFu);
-#pragma unroll 1
-                for (int half = 0; half < 2; half++) {
-                    const int slot = idx % kFineNS, use = idx / kFineNS;
-                    if (use > 0 && !mbar_wait(b_empty + 8 * slot, (use - 1) & 1, ctl)) { ok = false; break; }
-                    const uint32_t dst = ring + slot * kKvTileB, bar = b_full + 8 * slot;
-                    const CUtensorMap* map = half ? &tv : &tk;
-                    mbar_expect_tx(bar, kKvTileB);
-                    tma_load4(dst, map, bar, 0, tile * TE, bh, 0);
-                    tma_load4(dst + kKvPanelB, map, bar, 64, tile * TE, bh, 0);
-                    idx++;
-                }
+                load(j, true);
+                if (j + 2 < nent) load(j + 2, false);
             }
             mbar_wait(b_q, 0, ctl);
             for (int s = 0; s < kFineNS && s < idx; s++) {
@@ -482,37 +498,44 @@ fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 1);
         bool ok = mbar_wait(b_q, 0, ctl);
         tc_fence_after();
+        // ring index of K_j and V_j in the producer's order K0 K1 V0 K2 V1 ... V_{n-2} V_{n-1}
+        auto idx_k = [&](int j) { return j < 2 ? j : 2 * j - 1; };
+        auto idx_v = [&](int j) { return j == nent - 1 ? 2 * nent - 1 : 2 * j + 2; };
+        const uint64_t a0 = umma_desc_sw128(sQ, 16, 1024);
+        // S buffer (j & 1) = Q . K_j^T, then release K_j's slot
+        auto qk = [&](int j) -> bool {
+            const int ik = idx_k(j), slot = ik % kFineNS;
+            if (!mbar_wait(b_full + 8 * slot, (ik / kFineNS) & 1, ctl)) return false;
+            tc_fence_after();
+            const uint64_t b0 = umma_desc_sw128(ring + slot * kKvTileB, 16, 1024);
+            asm volatile(
+                "{\n\t.reg .pred pt, pf;\n\t.reg .b64 a, b;\n\t"
+                "setp.ne.b32 pf, %3, %3;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+                "add.s64 a, %1, 2;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                "add.s64 a, %1, 4;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                "add.s64 a, %1, 6;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                "add.s64 a, %1, 1024;\n\tadd.s64 b, %2, 512;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                "add.s64 a, %1, 1026;\n\tadd.s64 b, %2, 514;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                "add.s64 a, %1, 1028;\n\tadd.s64 b, %2, 516;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                "add.s64 a, %1, 1030;\n\tadd.s64 b, %2, 518;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+                "}"
+                ::"r"(tbase + 64u * (uint32_t)(j & 1)), "l"(a0), "l"(b0), "r"(idesc_qk)
+                : "memory");
+            umma_commit(b_s + 8 * (j & 1));
+            umma_commit(b_empty + 8 * slot);
+            return true;
+        };
+        if (ok && nent > 0) ok = qk(0);
+        if (ok && nent > 1) ok = qk(1);
 #pragma unroll 1
         for (int j = 0; j < nent && ok; j++) {
-            const int ik = 2 * j, iv = 2 * j + 1;
-            const int slotK = ik % kFineNS, slotV = iv % kFineNS;
-            if (!mbar_wait(b_full + 8 * slotK, (ik / kFineNS) & 1, ctl)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t sK = ring + slotK * kKvTileB, sV = ring + slotV * kKvTileB;
-            {
-                const uint64_t a0 = umma_desc_sw128(sQ, 16, 1024), b0 = umma_desc_sw128(sK, 16, 1024);
-                asm volatile(
-                    "{\n\t.reg .pred pt, pf;\n\t.reg .b64 a, b;\n\t"
-                    "setp.ne.b32 pf, %3, %3;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
-                    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
-                    "add.s64 a, %1, 2;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                    "add.s64 a, %1, 4;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                    "add.s64 a, %1, 6;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                    "add.s64 a, %1, 1024;\n\tadd.s64 b, %2, 512;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                    "add.s64 a, %1, 1026;\n\tadd.s64 b, %2, 514;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                    "add.s64 a, %1, 1028;\n\tadd.s64 b, %2, 516;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                    "add.s64 a, %1, 1030;\n\tadd.s64 b, %2, 518;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                    "}"
-                    ::"r"(tbase), "l"(a0), "l"(b0), "r"(idesc_qk)
-                    : "memory");
-            }
-            umma_commit(b_s);
-            umma_commit(b_empty + 8 * slotK);
+            const int iv = idx_v(j), slotV = iv % kFineNS;
             if (!mbar_wait(b_full + 8 * slotV, (iv / kFineNS) & 1, ctl)) { ok = false; break; }
-            if (!mbar_wait(b_p, j & 1, ctl)) { ok = false; break; }
+            if (!mbar_wait(b_p + 8 * (j & 1), (j >> 1) & 1, ctl)) { ok = false; break; }
             tc_fence_after();
             {
-                const uint64_t b0 = umma_desc_sw128(sV, kKvPanelB, 1024);
+                const uint64_t b0 = umma_desc_sw128(ring + slotV * kKvTileB, kKvPanelB, 1024);
                 asm volatile(
                     "{\n\t.reg .pred pt, p0;\n\t.reg .b64 b;\n\t.reg .b32 t;\n\t"
                     "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
@@ -521,11 +544,13 @@ fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
                     "add.u32 t, %1, 16;\n\tadd.s64 b, %2, 256;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
                     "add.u32 t, %1, 24;\n\tadd.s64 b, %2, 384;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
                     "}"
-                    ::"r"(tbase + 128u), "r"(tbase), "l"(b0), "r"(idesc_pv), "r"((uint32_t)(j > 0))
+                    ::"r"(tbase + 128u), "r"(tbase + 64u * (uint32_t)(j & 1)), "l"(b0), "r"(idesc_pv), "r"((uint32_t)(j > 0))
                     : "memory");
             }
+            umma_commit(b_od);
             umma_commit(b_empty + 8 * slotV);
             if (j == nent - 1) umma_commit(b_o);
+            if (j + 2 < nent) ok = qk(j + 2);  // into the buffer P.V_j just read (same thread: in order)
         }
         umma_commit(b_drain);
         mbar_wait(b_drain, 0, ctl);
