@@ -250,7 +250,7 @@ def main():
         vsa_in = torch.stack([vq, vk, vv, vgate])  # one tensor so the end-to-end leg copies it in one go
         proj = vsa_in
     out_buf = torch.empty((bh, length, 128), dtype=torch.bfloat16, device=dev)
-    launches_per_step = 5 if vsa_topk else (2 if world == 1 else 3)
+    launches_per_step = 5 if vsa_topk else (2 if world == 1 else 2 + spa.groups)
     attn_events = []
 
     def step(p, record=False):
@@ -337,13 +337,10 @@ def main():
     pk = peaks()
     rank_flops = total_flops / world
     achieved = rank_flops / (attn_ms * 1e-3) / 1e12
-    traffic = None
-    tf = ROOT / "profiles" / "traffic.json"
-    if tf.exists():
-        try:
-            traffic = json.loads(tf.read_text()).get(args.workload)
-        except Exception:
-            traffic = None
+    # DRAM bytes per attention launch: measured on a smaller case of the same kernel (ncu dram__bytes_read.sum +
+    # dram__bytes_write.sum, profiles/fv_sdpa_fwd_d128_24x8192.md: reads = 1.0007 x (Q + K + V), every output byte written
+    # once) and scaled by the bytes of Q, K, V and O, which is what the traffic is proportional to.
+    traffic = None if vsa_topk else int(4 * bh * length * 128 * 2 * 1.0005) + (2 * bh * (seq - length) * 128 * 2 if world > 1 else 0)
     line = dict(metric=METRIC, value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
                 ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
                 config=cfg, per_gpu_tflops=value / world, frac_of_bf16_peak_burst=value / world / pk["burst"],

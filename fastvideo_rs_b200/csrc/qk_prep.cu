@@ -50,7 +50,8 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 // One CTA per token row (b, s); thread t owns elements 8t..8t+7 of the heads*128 row, i.e.
 // 8 consecutive dims of head (8t)/128.  blockDim.x = heads*16.
-__global__ void __launch_bounds__(1024) fv_wan_qk_prep_kernel(const Params p) {
+template <int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_kernel(const Params p) {
     extern __shared__ float red[];  // [2][nwarps]
     const int row = blockIdx.x;     // b*seq + s
     const int b = row / p.seq, s = row % p.seq;
@@ -64,6 +65,27 @@ __global__ void __launch_bounds__(1024) fv_wan_qk_prep_kernel(const Params p) {
     if (p.v_out && act) {
         const uint4 v = *reinterpret_cast<const uint4*>(src + p.col_v + 8 * t);
         *reinterpret_cast<uint4*>(p.v_out + dst) = v;
+    }
+    // Everything the row needs is requested before the reduction, so the kernel pays one memory round trip, not three:
+    // rope factors (cos at the even index, sin at the odd one of each pair; the tables repeat each value twice) and weights.
+    float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+    float wqv[8], wkv[8];
+    if (act) {
+        if (p.cosv) {
+            const float4* cp = reinterpret_cast<const float4*>(p.cosv + (size_t)s * kD + pd);
+            const float4* sp = reinterpret_cast<const float4*>(p.sinv + (size_t)s * kD + pd);
+            const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+            cs[0] = c0.x; cs[1] = c0.z; cs[2] = c1.x; cs[3] = c1.z;
+            sn[0] = s0.y; sn[1] = s0.w; sn[2] = s1.y; sn[3] = s1.w;
+        }
+        if (p.q_out) {
+            const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.wq + 8 * t)), w1 = __ldg(reinterpret_cast<const float4*>(p.wq + 8 * t + 4));
+            wqv[0] = w0.x; wqv[1] = w0.y; wqv[2] = w0.z; wqv[3] = w0.w; wqv[4] = w1.x; wqv[5] = w1.y; wqv[6] = w1.z; wqv[7] = w1.w;
+        }
+        if (p.k_out) {
+            const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.wk + 8 * t)), w1 = __ldg(reinterpret_cast<const float4*>(p.wk + 8 * t + 4));
+            wkv[0] = w0.x; wkv[1] = w0.y; wkv[2] = w0.z; wkv[3] = w0.w; wkv[4] = w1.x; wkv[5] = w1.y; wkv[6] = w1.z; wkv[7] = w1.w;
+        }
     }
     float xq[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, xk[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float sq = 0.f, sk = 0.f;
@@ -103,19 +125,9 @@ __global__ void __launch_bounds__(1024) fv_wan_qk_prep_kernel(const Params p) {
         denom = (float)(p.heads * kD);
     }
     if (!act) return;
-    float cs[8], sn[8];
-    if (p.cosv) {
-        const float4* cp = reinterpret_cast<const float4*>(p.cosv + (size_t)s * kD + pd);
-        const float4* sp = reinterpret_cast<const float4*>(p.sinv + (size_t)s * kD + pd);
-        const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
-        cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
-        sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
-    }
-    auto finish = [&](const float (&x)[8], float ss, const float* w, __nv_bfloat16* out) {
+    auto finish = [&](const float (&x)[8], float ss, const float (&wv)[8], __nv_bfloat16* out) {
         const float ms = __fdiv_rn(ss, denom);
         const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, p.eps)));
-        const float4 w0 = *reinterpret_cast<const float4*>(w + 8 * t), w1 = *reinterpret_cast<const float4*>(w + 8 * t + 4);
-        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
         float y[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) y[i] = __fmul_rn(__fmul_rn(x[i], inv), wv[i]);
@@ -123,7 +135,7 @@ __global__ void __launch_bounds__(1024) fv_wan_qk_prep_kernel(const Params p) {
         if (p.cosv) {
 #pragma unroll
             for (int i = 0; i < 8; i += 2) {
-                const float c = cs[i], sv = sn[i + 1];
+                const float c = cs[i >> 1], sv = sn[i >> 1];
                 o[i] = __fsub_rn(__fmul_rn(y[i], c), __fmul_rn(y[i + 1], sv));
                 o[i + 1] = __fadd_rn(__fmul_rn(y[i], sv), __fmul_rn(y[i + 1], c));
             }
@@ -134,8 +146,8 @@ __global__ void __launch_bounds__(1024) fv_wan_qk_prep_kernel(const Params p) {
         *reinterpret_cast<uint4*>(out + dst) =
             make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
     };
-    if (p.q_out) finish(xq, sq, p.wq, p.q_out);
-    if (p.k_out) finish(xk, sk, p.wk, p.k_out);
+    if (p.q_out) finish(xq, sq, wqv, p.q_out);
+    if (p.k_out) finish(xk, sk, wkv, p.k_out);
 }
 
 }  // namespace fvprep
@@ -182,7 +194,11 @@ extern "C" int fv_wan_qk_prep_bf16(void* stream, const void* proj, int width, in
     p.per_head = norm_scope == FV_NORM_PER_HEAD;
     const int threads = (heads * 16 + 31) & ~31;
     const size_t smem = 2 * (threads / 32 + 1) * sizeof(float);
-    fvprep::fv_wan_qk_prep_kernel<<<(unsigned)(batch * seq), threads, smem, (cudaStream_t)stream>>>(p);
+    // up to 40 heads: 640-thread blocks, two per SM (register cap 51); beyond: one block of up to 1024 threads
+    if (threads <= 640)
+        fvprep::fv_wan_qk_prep_kernel<640, 2><<<(unsigned)(batch * seq), threads, smem, (cudaStream_t)stream>>>(p);
+    else
+        fvprep::fv_wan_qk_prep_kernel<1024, 1><<<(unsigned)(batch * seq), threads, smem, (cudaStream_t)stream>>>(p);
     FV_CUDA(cudaGetLastError());
     return FV_RAN;
 }

@@ -95,9 +95,14 @@ class SpLayout:
 
 
 class SpAttention:
-    """Sequence-parallel dense attention for one (seq, bh) shape; buffers allocated once."""
+    """Sequence-parallel dense attention for one (seq, bh) shape; buffers allocated once.
 
-    def __init__(self, seq: int, bh: int, group=None, device=None):
+    groups: the heads are cut into that many contiguous groups, each with its own pair of all-gathers; the remote pass
+    of group g starts when group g has arrived, so only the first group's exchange has to hide under the local pass
+    (at 8 GPUs the whole exchange is longer than the local pass).  Default: 2 groups from 8 ranks on, else 1."""
+
+    def __init__(self, seq: int, bh: int, group=None, device=None, groups: Optional[int] = None):
+        import os
         import torch.distributed as dist
         self.dist = dist
         self.group = group
@@ -109,14 +114,20 @@ class SpAttention:
         self.ranges, self.start, self.len, self.seg_rows = (self.layout.ranges, self.layout.start, self.layout.len,
                                                             self.layout.seg_rows)
         d = 128
+        if groups is None:
+            groups = int(os.environ.get("FV_SP_GROUPS", "0")) or (2 if self.world >= 8 else 1)
+        if groups < 1 or bh % groups != 0:
+            groups = 1
+        self.groups, self.bh_g = groups, bh // groups
         if self.world > 1:
-            self.k_all = torch.zeros((self.world, bh, self.seg_rows, d), dtype=torch.bfloat16, device=self.device)
-            self.v_all = torch.zeros_like(self.k_all)
+            mk = lambda: torch.zeros((self.world, self.bh_g, self.seg_rows, d), dtype=torch.bfloat16, device=self.device)
+            self.k_all = [mk() for _ in range(groups)]
+            self.v_all = [mk() for _ in range(groups)]
             self.o1 = torch.empty((bh, self.len, d), dtype=torch.float32, device=self.device)
             self.lse1 = torch.empty((bh, self.len), dtype=torch.float32, device=self.device)
             self.comm_stream = torch.cuda.Stream(device=self.device)
             self.pad = None
-            if self.len != self.seg_rows:
+            if self.layout.needs_padding():
                 self.pad = (torch.zeros((bh, self.seg_rows, d), dtype=torch.bfloat16, device=self.device),
                             torch.zeros((bh, self.seg_rows, d), dtype=torch.bfloat16, device=self.device))
 
@@ -134,19 +145,28 @@ class SpAttention:
             ks, vs = self.pad
         else:
             ks, vs = k, v
+        if out is None:
+            out = torch.empty((self.bh, self.len, d), dtype=torch.bfloat16, device=q.device)
+        G, n = self.groups, self.bh_g
         ready = torch.cuda.Event()
         ready.record(cur)
+        arrived = []
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ready)
-            self.dist.all_gather_into_tensor(self.k_all.view(-1, self.seg_rows, d), ks, group=self.group)
-            self.dist.all_gather_into_tensor(self.v_all.view(-1, self.seg_rows, d), vs, group=self.group)
-            gathered = torch.cuda.Event()
-            gathered.record(self.comm_stream)
-        # pass 1: the local keys, while the exchange is in flight
+            for g in range(G):
+                self.dist.all_gather_into_tensor(self.k_all[g].view(-1, self.seg_rows, d), ks[g * n:(g + 1) * n], group=self.group)
+                self.dist.all_gather_into_tensor(self.v_all[g].view(-1, self.seg_rows, d), vs[g * n:(g + 1) * n], group=self.group)
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+                arrived.append(ev)
+        # pass 1: the local keys, every head, while the exchange is in flight
         l1, s1 = self.layout.pass1()
         segments_fwd(q, ks, vs, l1, s1, self.seg_rows, scale, out=self.o1, lse_out=self.lse1)
-        cur.wait_event(gathered)
-        # pass 2: every other rank's keys, merged with pass 1
+        # pass 2 per head group, as it arrives: every other rank's keys, merged with pass 1
         l2, s2 = self.layout.pass2()
-        return segments_fwd(q, self.k_all, self.v_all, l2, s2, self.seg_rows, scale, out=out,
-                            prev_o=self.o1, prev_lse=self.lse1)
+        for g in range(G):
+            cur.wait_event(arrived[g])
+            sl = slice(g * n, (g + 1) * n)
+            segments_fwd(q[sl], self.k_all[g], self.v_all[g], l2, s2, self.seg_rows, scale, out=out[sl],
+                         prev_o=self.o1[sl], prev_lse=self.lse1[sl])
+        return out
