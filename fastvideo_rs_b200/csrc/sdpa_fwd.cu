@@ -11,13 +11,13 @@ constexpr int kStages = 4;
 
 // One entry per softmax variant (see sdpa_body); FV_SDPA_VARIANT picks one at run time for A/B timing,
 // kDefaultVariant otherwise.
-template <int VAR, bool MASKED>
+template <int VAR, bool MASKED, bool SPLITP = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fv_sdpa_fwd_d128(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                  const __grid_constant__ CUtensorMap tv, const __grid_constant__ Params p) {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL)
     extern __shared__ __align__(1024) unsigned char fv_smem[];
-    sdpa_body<kStages, VAR, MASKED>(&tq, &tk, &tv, p, fv_smem);
+    sdpa_body<kStages, VAR, MASKED, SPLITP>(&tq, &tk, &tv, p, fv_smem);
 #endif
 }
 
@@ -38,6 +38,8 @@ constexpr int kDefaultVariant = 13;
 typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const Params);
 static KernelFn kernel_for(int var, bool masked) {
     switch (var) {
+        case 213: return masked ? fv_sdpa_fwd_d128<13, true, true> : fv_sdpa_fwd_d128<13, false, true>;  // 13 + split P
+        case 200: return masked ? fv_sdpa_fwd_d128<0, true, true> : fv_sdpa_fwd_d128<0, false, true>;     // 0 + split P
         case 100: return masked ? fv_sdpa_fwd64_d128<0, true> : fv_sdpa_fwd64_d128<0, false>;
         case 101: return masked ? fv_sdpa_fwd64_d128<1, true> : fv_sdpa_fwd64_d128<1, false>;
         case 1: return masked ? fv_sdpa_fwd_d128<1, true> : fv_sdpa_fwd_d128<1, false>;

@@ -129,6 +129,23 @@ FV_DEV void issue_pv(uint32_t tO, uint32_t tP, uint32_t sV, bool acc) {
         : "memory");
 }
 
+// Half of issue_pv: keys 64*half .. 64*half+63 (four K=16 steps).
+FV_DEV void issue_pv_part(uint32_t tO, uint32_t tP, uint32_t sV, bool acc, int half) {
+    constexpr uint32_t idesc = fvp::umma_idesc_bf16(128, 128, 1);
+    const uint64_t b0 = fvp::umma_desc_sw128(sV + 8192u * (uint32_t)half, kPanelB, 1024);
+    const uint32_t tPh = tP + 32u * (uint32_t)half;
+    asm volatile(
+        "{\n\t.reg .pred pt, p0;\n\t.reg .b64 b;\n\t.reg .b32 t;\n\t"
+        "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+        "add.u32 t, %1, 8;\n\tadd.s64 b, %2, 128;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
+        "add.u32 t, %1, 16;\n\tadd.s64 b, %2, 256;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
+        "add.u32 t, %1, 24;\n\tadd.s64 b, %2, 384;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
+        "}"
+        ::"r"(tO), "r"(tPh), "l"(b0), "r"(idesc), "r"((uint32_t)acc)
+        : "memory");
+}
+
 FV_DEV float u2f(uint32_t u) { return __uint_as_float(u); }
 FV_DEV uint32_t f2u(float f) { return __float_as_uint(f); }
 
@@ -167,7 +184,7 @@ FV_DEV float row_max(const uint32_t (&u)[128]) {
 // PACK: two-wide FMA / ADD.  PMASK >= 0: the pairs w of each half with (w & PMASK) == PMASK go through the
 // FMA-pipe exponential (1 -> every second pair, 3 -> every fourth), the others through MUFU ex2.
 template <bool PACK, int PMASK, int ABL = 0>
-FV_DEV float exp_and_store(const uint32_t (&u)[128], float sl2, float noff, uint32_t tP) {
+FV_DEV float exp_and_store(const uint32_t (&u)[128], float sl2, float noff, uint32_t tP, uint32_t bar_half = 0u) {
     using namespace fvp;
     float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
     uint64_t ya = pack_f32x2(0.f, 0.f), yb = pack_f32x2(0.f, 0.f);
@@ -212,6 +229,11 @@ FV_DEV float exp_and_store(const uint32_t (&u)[128], float sl2, float noff, uint
         }
         if constexpr ((ABL & 16) == 0) tmem_st32(tP + 32u * h, pw);  // (ABL 16: timing ablation, P is not stored)
         else if (pw[0] == 0xdeadbeefu && pw[31] == 0x12345u) tmem_st32(tP + 32u * h, pw);
+        if (h == 0 && bar_half != 0u) {  // hand the first 64 keys over
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(bar_half);
+        }
     }
     if constexpr (PACK) {
         unpack_f32x2(ya, y0, y1);
@@ -225,7 +247,9 @@ FV_DEV float exp_and_store(const uint32_t (&u)[128], float sl2, float noff, uint
 // 8 = three-input max; 16 = exponentials against the current reference before the row maximum is known (P stored speculatively);
 // 32 = the same in registers, stored only once it is known to stand, row sum after the signal.
 // MASKED = false compiles the block-causal bookkeeping out (dense calls: fewer live registers in the softmax loop).
-template <int NS, int VAR, bool MASKED>
+// SPLITP: P is handed to the MMA thread in two halves (keys 0-63, then 64-127), so P.V starts while the second half of
+// the exponentials is still being computed.
+template <int NS, int VAR, bool MASKED, bool SPLITP = false>
 FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtensorMap* tv, const Params& p,
                       unsigned char* smem_raw) {
     using namespace fvp;
@@ -240,7 +264,8 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
     const uint32_t b_s = b_empty + 8 * NS;
     const uint32_t b_p = b_s + 16;
     const uint32_t b_o = b_p + 16;
-    const uint32_t b_drain = b_o + 16;
+    const uint32_t b_pa = b_o + 16;   // first half of P stored (SPLITP)
+    const uint32_t b_drain = b_pa + 16;
     const uint32_t tslot = b_drain + 8;
     const uint32_t aflag = tslot + 4;
     volatile uint32_t* tslot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tslot - raw));
@@ -263,6 +288,7 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
             mbar_init(b_s + 8 * i, 1);
             mbar_init(b_p + 8 * i, 128);
             mbar_init(b_o + 8 * i, 1);
+            mbar_init(b_pa + 8 * i, 128);
         }
         mbar_init(b_drain, 1);
         // A CTA that starts after another one gave up does nothing.
@@ -448,8 +474,8 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
             float rowsum;
             // (warp-uniform choice: the TMEM store inside is warp-collective and must not sit in divergent code)
             if (kPolyMask >= 0 && __all_sync(0xffffffffu, full_tile))
-                rowsum = exp_and_store<(VAR & 1) != 0, kPolyMask, (VAR >> 6)>(u, sl2, noff, tP);
-            else rowsum = exp_and_store<(VAR & 1) != 0, -1, (VAR >> 6)>(u, sl2, noff, tP);
+                rowsum = exp_and_store<(VAR & 1) != 0, kPolyMask, (VAR >> 6)>(u, sl2, noff, tP, SPLITP ? b_pa + 8 * tile : 0u);
+            else rowsum = exp_and_store<(VAR & 1) != 0, -1, (VAR >> 6)>(u, sl2, noff, tP, SPLITP ? b_pa + 8 * tile : 0u);
             l = fmaf(l, a, rowsum);
             }
             tmem_st_wait();
@@ -603,10 +629,18 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
                     const uint32_t sV = ring + slotV * kTileB;
 #pragma unroll
                     for (int i = 0; i < 2; i++) {
+                        if constexpr (SPLITP) {
+                            if (ok && !mbar_wait(b_pa + 8 * i, (it - 1) & 1, ctl)) ok = false;
+                            if (ok) {
+                                tc_fence_after();
+                                issue_pv_part(tbase + 256u + 128u * i, tbase + 128u * i, sV, it > 1, 0);
+                            }
+                        }
                         if (ok && !mbar_wait(b_p + 8 * i, (it - 1) & 1, ctl)) ok = false;
                         if (ok) {
                             tc_fence_after();
-                            if constexpr (((VAR >> 6) & 64) == 0) issue_pv(tbase + 256u + 128u * i, tbase + 128u * i, sV, it > 1);
+                            if constexpr (SPLITP) issue_pv_part(tbase + 256u + 128u * i, tbase + 128u * i, sV, true, 1);
+                            else if constexpr (((VAR >> 6) & 64) == 0) issue_pv(tbase + 256u + 128u * i, tbase + 128u * i, sV, it > 1);
                             if constexpr (((VAR >> 6) & 32) == 0) issue_qk(tbase + 128u * i, sQ + i * kTileB, sK);
                             umma_commit(b_s + 8 * i);
                         }
@@ -622,10 +656,18 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
                 const uint32_t sV = ring + slotV * kTileB;
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
+                    if constexpr (SPLITP) {
+                        if (ok) ok = mbar_wait(b_pa + 8 * i, (it - 1) & 1, ctl);
+                        if (ok) {
+                            tc_fence_after();
+                            issue_pv_part(tbase + 256u + 128u * i, tbase + 128u * i, sV, it > 1, 0);
+                        }
+                    }
                     if (ok) ok = mbar_wait(b_p + 8 * i, (it - 1) & 1, ctl);
                     if (ok) {
                         tc_fence_after();
-                        issue_pv(tbase + 256u + 128u * i, tbase + 128u * i, sV, it > 1);
+                        if constexpr (SPLITP) issue_pv_part(tbase + 256u + 128u * i, tbase + 128u * i, sV, true, 1);
+                        else issue_pv(tbase + 256u + 128u * i, tbase + 128u * i, sV, it > 1);
                         umma_commit(b_o + 8 * i);
                     }
                 }
