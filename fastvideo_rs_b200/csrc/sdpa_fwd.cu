@@ -32,9 +32,9 @@ fv_sdpa_fwd64_d128(const __grid_constant__ CUtensorMap tq, const __grid_constant
 #endif
 }
 
-// 13 = packed f32x2 arithmetic + a quarter of the exponentials of unmasked tiles on the FMA pipe + three-input
-// max: the fastest of the measured mixes (profiles/fv_sdpa_variants.md).
-constexpr int kDefaultVariant = 13;
+// 213 = softmax mix 13 (packed f32x2 arithmetic + a quarter of the exponentials of unmasked tiles on the FMA pipe +
+// three-input max) with P handed over in two halves: the fastest of the measured mixes (profiles/fv_sdpa_variants.md).
+constexpr int kDefaultVariant = 213;
 typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const Params);
 static KernelFn kernel_for(int var, bool masked) {
     switch (var) {
