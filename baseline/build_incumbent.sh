@@ -3,9 +3,10 @@
 # repository is measured against) from the read-only reference tree, where its sources lie, into the
 # git-ignored baseline/_ref/.  Nothing of the reference is copied into this repository.  Recipe:
 # scripts/gpu/upstream/pod.sh:221-246 of the reference, without its -DDC_DEBUG_HANG debug build.
-#   usage: baseline/build_incumbent.sh [reference root, default /root/reference]
+#   usage: baseline/build_incumbent.sh <reference root>     (or FV_REFERENCE_ROOT=<reference root>)
 set -e
-REF=${1:-/root/reference}
+REF=${1:-${FV_REFERENCE_ROOT:-}}
+[ -n "$REF" ] || { echo "usage: $0 <reference root>"; exit 2; }
 HERE=$(cd "$(dirname "$0")" && pwd)
 SRC=$REF/scripts/gpu/upstream/attn_dc_bench.cu
 [ -f "$SRC" ] || { echo "no reference tree at $REF: nothing built"; exit 0; }

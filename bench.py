@@ -44,7 +44,16 @@ WORKLOADS = {
                                   "sigmoid gate applied to seeded logits before the call"),
     "tiny": dict(batch=1, heads=12, grid=(3, 8, 8), block=0, desc="tiny Wan-arch dense self-attention (192 tokens)"),
 }
-METRIC = "Wan self-attn TFLOP/s (prologue + attention), whole job"
+def _metric_name():
+    """The metric string of the benchmark contract file when it sits beside this script."""
+    try:
+        return json.loads((ROOT / "BASELINE.json").read_text())["metric"]
+    except Exception:
+        return "Wan self-attn TFLOP/s/GPU (% of BF16 peak), dense+VSA, at 1/2/4/8 B200"
+
+
+METRIC = _metric_name()
+UNIT_NOTE = "value = whole-job TFLOP/s (prologue + attention); per GPU in per_gpu_tflops, fraction of peak in frac_of_bf16_peak_*"
 
 
 def peaks():
@@ -338,12 +347,12 @@ def main():
     rank_flops = total_flops / world
     achieved = rank_flops / (attn_ms * 1e-3) / 1e12
     # DRAM bytes per attention launch: measured on a smaller case of the same kernel (ncu dram__bytes_read.sum +
-    # dram__bytes_write.sum, profiles/fv_sdpa_fwd_d128_24x8192.md: reads = 1.0007 x (Q + K + V), every output byte written
+    # dram__bytes_write.sum of a 24-head x 8192-token capture: reads = 1.0007 x (Q + K + V), every output byte written
     # once) and scaled by the bytes of Q, K, V and O, which is what the traffic is proportional to.
     traffic = None if vsa_topk else int(4 * bh * length * 128 * 2 * 1.0005) + (2 * bh * (seq - length) * 128 * 2 if world > 1 else 0)
     line = dict(metric=METRIC, value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
                 ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
-                config=cfg, per_gpu_tflops=value / world, frac_of_bf16_peak_burst=value / world / pk["burst"],
+                config=cfg, value_note=UNIT_NOTE, per_gpu_tflops=value / world, frac_of_bf16_peak_burst=value / world / pk["burst"],
                 frac_of_bf16_peak_sustained=value / world / pk["sustained"], peaks=pk,
                 roofline=dict(bound="tensor", kernel="fv_vsa_fine_kernel (+4 small kernels in the timed span)" if vsa_topk else "fv_sdpa_fwd_d128",
                               achieved=achieved, peak=pk["sustained"], unit="TFLOP/s",

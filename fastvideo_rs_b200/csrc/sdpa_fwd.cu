@@ -33,7 +33,8 @@ fv_sdpa_fwd64_d128(const __grid_constant__ CUtensorMap tq, const __grid_constant
 }
 
 // 213 = softmax mix 13 (packed f32x2 arithmetic + a quarter of the exponentials of unmasked tiles on the FMA pipe +
-// three-input max) with P handed over in two halves: the fastest of the measured mixes (profiles/fv_sdpa_variants.md).
+// three-input max) with P handed over in two halves: the fastest of the mixes measured
+// on B200 (A/B with FV_SDPA_VARIANT and the native checker's --bench mode).
 constexpr int kDefaultVariant = 213;
 typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const Params);
 static KernelFn kernel_for(int var, bool masked) {

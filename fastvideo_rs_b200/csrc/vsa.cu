@@ -218,10 +218,6 @@ struct FineParams {
     int list_cap;
 };
 
-__host__ __device__ inline uint32_t fine_smem_bytes(int list_cap) {
-    return 1024u + kQTileB + kFineNS * kKvTileB + 256u + 4u * (uint32_t)(list_cap + 2 * 0) + 8u * 0;
-}
-
 __global__ void __launch_bounds__(kFineThreads, 2)
 fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                    const __grid_constant__ CUtensorMap tv, const __grid_constant__ FineParams p) {
@@ -286,8 +282,7 @@ fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         const uint32_t* la = p.selected + ((size_t)bh * p.nt + qt0) * p.topk;
         const uint32_t* lb = p.selected + ((size_t)bh * p.nt + qt1) * p.topk;
         const int na = p.topk, nb = qt1 < p.nt ? p.topk : 0;
-        // stage both lists behind the union area (the union never overtakes what it still has to read:
-        // it is built in place from the front while the sources sit at the back of the area)
+        // both selections are staged in shared memory behind the union area, then merged by one lane
         volatile uint32_t* sa = list + p.list_cap;
         volatile uint32_t* sb = sa + p.topk;
         for (int i = lane; i < na; i += 32) sa[i] = la[i];
