@@ -84,7 +84,7 @@ static int chosen_variant() {
 static int launch(cudaStream_t stream, const void* q, const void* k, const void* v, void* out, int out_is_bf16, int bh,
                   int sq, int nseg, const int* seg_len, const int* seg_start, int seg_rows, float scale, int mask_mode,
                   int block_tokens, int window, int sink, int q_row0, float* lse_out, const float* prev_o,
-                  const float* prev_lse, int* status_in = nullptr) {
+                  const float* prev_lse, int* status_in = nullptr, int out_heads = 0) {
     int dev;
     int rc = fvrt::require_sm100(&dev);
     if (rc != FV_RAN) return rc;
@@ -107,6 +107,7 @@ static int launch(cudaStream_t stream, const void* q, const void* k, const void*
     p.prev_o = prev_o;
     p.prev_lse = prev_lse;
     p.out_is_bf16 = out_is_bf16 ? 1 : 0;
+    p.out_heads = out_heads;
     p.bh = bh;
     p.sq = sq;
     p.nqb = (sq + kRowsPerCta - 1) / kRowsPerCta;
@@ -256,4 +257,15 @@ extern "C" int fv_sdpa_dense_bf16(void* stream, const void* q, const void* k, co
     const int len = sk, start = 0;
     return fvsdpa::launch((cudaStream_t)stream, q, k, v, out, out_is_bf16, bh, sq, 1, &len, &start, sk, scale, mask_mode,
                           block_tokens, window, sink, q_row0, nullptr, nullptr, nullptr);
+}
+
+extern "C" int fv_sdpa_dense_merged_bf16(void* stream, const void* q, const void* k, const void* v, void* out,
+                                         int out_is_bf16, int batch, int heads, int sq, int sk, int d, float scale,
+                                         int mask_mode, int block_tokens, int window, int sink, int q_row0) {
+    fvrt::clear_error();
+    if (d != 128 || batch <= 0 || heads <= 0 || sq <= 0 || sk <= 0) return FV_DECLINED;
+    if (sq > 0x3fffffff || sk > 0x3fffffff || (long long)batch * heads > 0x7fffffffll) return FV_DECLINED;
+    const int len = sk, start = 0;
+    return fvsdpa::launch((cudaStream_t)stream, q, k, v, out, out_is_bf16, batch * heads, sq, 1, &len, &start, sk, scale,
+                          mask_mode, block_tokens, window, sink, q_row0, nullptr, nullptr, nullptr, nullptr, heads);
 }

@@ -50,6 +50,7 @@ struct Params {
     const float* prev_lse;  // its lse (same convention); both or neither
     int* status;            // device status word (0 = fine)
     int out_is_bf16;
+    int out_heads;           // 0: out is [bh, sq, 128]; h > 0: merged heads, out is [bh / h, sq, h * 128]
     int bh, sq, nqb;
     float sl2;
     int nseg;
@@ -511,7 +512,12 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
                     p.lse_out[rowi] = lse;
                 }
             }
-            const size_t off = rowi * kD;
+            const size_t off = rowi * kD;  // BHSD offset (earlier pass, lse)
+            size_t ooff = off;             // where this row's output goes
+            if (p.out_heads > 0) {
+                const int bb = bh / p.out_heads, hh = bh % p.out_heads;
+                ooff = (((size_t)bb * p.sq + (live ? qr : 0)) * p.out_heads + hh) * kD;
+            }
 #pragma unroll 1
             for (int q = 0; q < 4; q++) {
                 uint32_t o[32];
@@ -539,13 +545,13 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
                     }
                 }
                 if (p.out_is_bf16) {
-                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.out) + off + 32 * q);
+                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.out) + ooff + 32 * q);
 #pragma unroll
                     for (int c = 0; c < 4; c++)
                         dst[c] = make_uint4(pack_bf16x2(f[8 * c], f[8 * c + 1]), pack_bf16x2(f[8 * c + 2], f[8 * c + 3]),
                                             pack_bf16x2(f[8 * c + 4], f[8 * c + 5]), pack_bf16x2(f[8 * c + 6], f[8 * c + 7]));
                 } else {
-                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + off + 32 * q);
+                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + ooff + 32 * q);
 #pragma unroll
                     for (int c = 0; c < 8; c++) dst[c] = make_float4(f[4 * c], f[4 * c + 1], f[4 * c + 2], f[4 * c + 3]);
                 }

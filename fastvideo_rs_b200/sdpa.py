@@ -141,6 +141,27 @@ def dense_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: Optio
     return out
 
 
+def dense_fwd_merged(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: Optional[float] = None,
+                     out_bf16: bool = True, causal: Optional[BlockCausal] = None) -> torch.Tensor:
+    """dense_fwd on BHSD q [b, h, sq, 128], k / v [b, h, sk, 128] with the head merge folded into the store:
+    returns [b, sq, h * 128] (what merge_heads gives, rt/ops.rs:2373-2385)."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _check_bf16_cuda(n, t)
+    if q.dim() != 4 or k.dim() != 4 or v.shape != k.shape or k.shape[:2] != q.shape[:2] or k.shape[3] != q.shape[3]:
+        raise ValueError("sdpa expects BHSD")
+    b, h, sq, d = q.shape
+    sk = k.shape[2]
+    scale = float(scale) if scale is not None else 1.0 / d ** 0.5
+    out = torch.empty((b, sq, h * d), dtype=torch.bfloat16 if out_bf16 else torch.float32, device=q.device)
+    mode, bt, win, sink = (1, causal.block_tokens, causal.window, causal.sink) if causal else (0, 0, 0, 0)
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().fv_sdpa_dense_merged_bf16(_stream_ptr(), ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()),
+                                                  ctypes.c_void_p(v.data_ptr()), ctypes.c_void_p(out.data_ptr()), int(out_bf16),
+                                                  b, h, sq, sk, d, ctypes.c_float(scale), mode, bt, win, sink, 0)
+    _lib.check(rc, "dense_fwd_merged")
+    return out
+
+
 def device_status() -> int:
     """Synchronises the current stream and returns the kernels' status word (0 = every bounded wait
     completed); raises FvError when a kernel gave up."""

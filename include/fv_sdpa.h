@@ -74,6 +74,15 @@ FV_API int fv_sdpa_dense_bf16(void* stream, const void* q, const void* k, const 
                        int bh, int sq, int sk, int d, float scale, int mask_mode, int block_tokens, int window,
                        int sink, int q_row0);
 
+/* fv_sdpa_dense_bf16 with the head merge folded into the output store: q, k, v as above with bh = batch * heads
+ * (head index fastest), out [batch, sq, heads * 128] -- the layout merge_heads produces
+ * (crates/fastvideo-cudarc/src/rt/kernels/core.cu:430-443, rt/ops.rs:2373-2385) and the output projection reads, so
+ * WanAttention::attend (crates/fastvideo-cudarc/src/wan/transformer.rs:180-192) needs no merge launch.
+ * Same values as fv_sdpa_dense_bf16, bit for bit, in another order. */
+FV_API int fv_sdpa_dense_merged_bf16(void* stream, const void* q, const void* k, const void* v, void* out,
+                                     int out_is_bf16, int batch, int heads, int sq, int sk, int d, float scale,
+                                     int mask_mode, int block_tokens, int window, int sink, int q_row0);
+
 /* The general form behind fv_sdpa_dense_bf16, used by the sequence-parallel path.
  * K and V are `nseg` segments (nseg <= FV_MAX_SEGMENTS), segment s holding seg_len[s]
  * keys whose global indices start at seg_start[s]; segment s of head h starts at element

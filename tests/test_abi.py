@@ -16,7 +16,7 @@ def declared_symbols():
 
 def test_header_declares_the_expected_surface():
     names = declared_symbols()
-    for must in ("fv_sdpa", "fv_sdpa_dense_bf16", "fv_sdpa_segments_bf16", "fv_wan_qk_prep_bf16", "fv_wan_rope_tables",
+    for must in ("fv_sdpa", "fv_sdpa_dense_bf16", "fv_sdpa_dense_merged_bf16", "fv_sdpa_two_pass_noalloc_bf16", "fv_sdpa_segments_bf16", "fv_wan_qk_prep_bf16", "fv_wan_rope_tables",
                  "fv_rule_dense_route", "fv_rule_mma_kernel", "fv_shard_ranges", "fv_last_error", "fv_device_status"):
         assert must in names
 

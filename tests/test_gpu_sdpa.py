@@ -186,6 +186,34 @@ def test_two_pass_segments_equal_one_pass(fvlib, oracle):
     assert np.abs(to_host_f32(lse) - want_lse).max() < 2e-2
 
 
+def test_merged_heads_output_is_the_permuted_bhsd_output(fvlib, oracle):
+    """merge_heads folded into the store (rt/ops.rs:2373-2385): same bits as the BHSD call, [b, s, h*d] order."""
+    from fastvideo_rs_b200 import sdpa
+    b, h, sq, sk = 2, 3, 300, 421
+    q, k, v = qkv(oracle, 25, b * h, sq, sk)
+    tq, tk, tv = (to_dev_bf16(x).view(b, h, -1, 128) for x in (q, k, v))
+    for bf16 in (True, False):
+        want = sdpa.dense_fwd(tq.view(b * h, sq, 128), tk.view(b * h, sk, 128), tv.view(b * h, sk, 128), out_bf16=bf16)
+        got = sdpa.dense_fwd_merged(tq, tk, tv, out_bf16=bf16)
+        assert got.shape == (b, sq, h * 128)
+        assert torch.equal(got, want.view(b, h, sq, 128).permute(0, 2, 1, 3).reshape(b, sq, h * 128))
+    bc = sdpa.BlockCausal(64, 0, 0)
+    want = sdpa.dense_fwd(tq.view(b * h, sq, 128), tk.view(b * h, sk, 128), tv.view(b * h, sk, 128), causal=bc)
+    got = sdpa.dense_fwd_merged(tq, tk, tv, causal=bc)
+    assert torch.equal(got, want.view(b, h, sq, 128).permute(0, 2, 1, 3).reshape(b, sq, h * 128))
+
+
+def test_relative_l2_error_is_inside_the_reference_kernel_bounds(fvlib, oracle):
+    """crates/fastvideo-gpucheck/src/kernels/attn2.rs:83-175,611-694: rel-L2 against the f32 reference <= 1e-2."""
+    from fastvideo_rs_b200 import sdpa
+    for bh, sq, sk in ((2, 2048, 2048), (2, 300, 512), (1, 63, 4097)):
+        q, k, v = qkv(oracle, 26 + sq, bh, sq, sk)
+        got = to_host_f32(sdpa.dense_fwd(to_dev_bf16(q), to_dev_bf16(k), to_dev_bf16(v), out_bf16=False)).astype(np.float64)
+        want = oracle.sdpa_rows_f64(q, k, v)
+        rel = np.sqrt(((got - want) ** 2).sum() / (want ** 2).sum())
+        assert rel <= 1e-2, rel
+
+
 def test_invalid_arguments_are_errors_not_launches(fvlib, oracle):
     from fastvideo_rs_b200 import FvError, sdpa
     q, k, v = (to_dev_bf16(x) for x in qkv(oracle, 24, 1, 64, 64))
