@@ -68,57 +68,104 @@ __global__ void __launch_bounds__(192) vsa_prep_kernel(const __nv_bfloat16* __re
 }
 
 // ------------------------------------------------------------------ 2. coarse scores (f64, in order)
-// grid (ceil(nt/16), ceil(nt/16), bh), 256 threads: thread (i, j) of a 16 x 16 block of (query tile,
-// key tile) pairs.
+// grid (ceil(nt/64), ceil(nt/64), bh), 256 threads: a 64 x 64 block of (query tile, key tile) pairs per CTA, a 4 x 4
+// patch per thread (shared-memory reads, not the FMAs, bound the 1 x 1 version).  Dynamic smem: 2 x 64 x 129 doubles.
+constexpr int kScoreTile = 64;
+constexpr size_t kScoreSmem = 2 * (size_t)kScoreTile * (kD + 1) * sizeof(double);
 __global__ void __launch_bounds__(256) vsa_scores_kernel(const float* __restrict__ qc, const float* __restrict__ kc, int nt,
                                                          float scale, float* __restrict__ scores) {
-    __shared__ float qs[16][kD + 1], ks[16][kD + 1];
-    const int bh = blockIdx.z, q0 = blockIdx.y * 16, k0 = blockIdx.x * 16;
-    for (int e = threadIdx.x; e < 16 * kD; e += 256) {
+    // the means widened to f64 once, on the way into shared memory (a conversion per use would cost more than the FMA)
+    extern __shared__ double score_smem[];
+    double (*qs)[kD + 1] = reinterpret_cast<double (*)[kD + 1]>(score_smem);
+    double (*ks)[kD + 1] = reinterpret_cast<double (*)[kD + 1]>(score_smem + (size_t)kScoreTile * (kD + 1));
+    const int bh = blockIdx.z, q0 = blockIdx.y * kScoreTile, k0 = blockIdx.x * kScoreTile;
+    for (int e = threadIdx.x; e < kScoreTile * kD; e += 256) {
         const int r = e / kD, c = e % kD;
-        qs[r][c] = (q0 + r < nt) ? qc[((size_t)bh * nt + q0 + r) * kD + c] : 0.f;
-        ks[r][c] = (k0 + r < nt) ? kc[((size_t)bh * nt + k0 + r) * kD + c] : 0.f;
+        qs[r][c] = (q0 + r < nt) ? (double)qc[((size_t)bh * nt + q0 + r) * kD + c] : 0.0;
+        ks[r][c] = (k0 + r < nt) ? (double)kc[((size_t)bh * nt + k0 + r) * kD + c] : 0.0;
     }
     __syncthreads();
-    const int i = threadIdx.x >> 4, j = threadIdx.x & 15;
-    double acc = 0.0;
-#pragma unroll 8
-    for (int d = 0; d < kD; d++) acc = fma((double)qs[i][d], (double)ks[j][d], acc);  // product exact: == mul then add
-    if (q0 + i < nt && k0 + j < nt) scores[((size_t)bh * nt + q0 + i) * nt + k0 + j] = (float)(acc * (double)scale);
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    double acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) acc[a][b] = 0.0;
+#pragma unroll 4
+    for (int d = 0; d < kD; d++) {
+        double qv[4], kv[4];
+#pragma unroll
+        for (int a = 0; a < 4; a++) {
+            qv[a] = qs[ty + 16 * a][d];
+            kv[a] = ks[tx + 16 * a][d];
+        }
+#pragma unroll
+        for (int a = 0; a < 4; a++)
+#pragma unroll
+            for (int b = 0; b < 4; b++) acc[a][b] = fma(qv[a], kv[b], acc[a][b]);  // product exact: == multiply then add, in index order
+    }
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const int qi = q0 + ty + 16 * a, kj = k0 + tx + 16 * b;
+            if (qi < nt && kj < nt) scores[((size_t)bh * nt + qi) * nt + kj] = (float)(acc[a][b] * (double)scale);
+        }
 }
 
 // ------------------------------------------------------------------ 3. coarse attention over tiles
-// grid (nt, bh), 128 threads (thread = output dim); dynamic smem: nt doubles.
+// grid (ceil(nt / kCoarseQT), bh), 128 threads (thread = output dim).  One CTA serves kCoarseQT query tiles so that each
+// row of the pooled V is read from L2 once per kCoarseQT outputs.  Softmax weights in f64 (max, exp, sum, divide as the
+// host does), kept as f32; out accumulated in f32 in tile order.  Dynamic smem: kCoarseQT * nt floats + nt doubles.
+constexpr int kCoarseQT = 4;
 __global__ void __launch_bounds__(128) vsa_coarse_kernel(const float* __restrict__ scores, const float* __restrict__ vc, int nt,
                                                          float* __restrict__ coarse) {
-    extern __shared__ double wexp[];
+    extern __shared__ double coarse_smem[];
+    double* ebuf = coarse_smem;                               // [nt]
+    float* wts = reinterpret_cast<float*>(coarse_smem + nt);  // [kCoarseQT][nt]
     __shared__ float redf[4];
     __shared__ double redd[4];
-    const int qt = blockIdx.x, bh = blockIdx.y, t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const float* s = scores + ((size_t)bh * nt + qt) * nt;
-    float m = -INFINITY;
-    for (int i = t; i < nt; i += 128) m = fmaxf(m, s[i]);
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if (lane == 0) redf[warp] = m;
-    __syncthreads();
-    m = fmaxf(fmaxf(redf[0], redf[1]), fmaxf(redf[2], redf[3]));
-    double z = 0.0;
-    for (int i = t; i < nt; i += 128) {
-        const double e = exp((double)(s[i] - m));
-        wexp[i] = e;
-        z += e;
+    const int qt0 = blockIdx.x * kCoarseQT, bh = blockIdx.y, t = threadIdx.x, lane = t & 31, warp = t >> 5;
+#pragma unroll 1
+    for (int q = 0; q < kCoarseQT; q++) {
+        const int qt = qt0 + q;
+        if (qt >= nt) break;  // CTA-uniform
+        const float* s = scores + ((size_t)bh * nt + qt) * nt;
+        float m = -INFINITY;
+        for (int i = t; i < nt; i += 128) m = fmaxf(m, s[i]);
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        __syncthreads();  // redf / redd / ebuf of the previous query tile are no longer read
+        if (lane == 0) redf[warp] = m;
+        __syncthreads();
+        m = fmaxf(fmaxf(redf[0], redf[1]), fmaxf(redf[2], redf[3]));
+        double z = 0.0;
+        for (int i = t; i < nt; i += 128) {
+            const double e = exp((double)(s[i] - m));
+            ebuf[i] = e;
+            z += e;
+        }
+        for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+        if (lane == 0) redd[warp] = z;
+        __syncthreads();
+        z = (redd[0] + redd[1]) + (redd[2] + redd[3]);
+        for (int i = t; i < nt; i += 128) wts[(size_t)q * nt + i] = (float)(ebuf[i] / z);
     }
-    for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
-    if (lane == 0) redd[warp] = z;
     __syncthreads();
-    z = (redd[0] + redd[1]) + (redd[2] + redd[3]);
-    for (int i = t; i < nt; i += 128) wexp[i] = wexp[i] / z;  // the weights, once (same f64 division as the host)
-    __syncthreads();
-    float acc = 0.f;
+    float acc[kCoarseQT];
+#pragma unroll
+    for (int q = 0; q < kCoarseQT; q++) acc[q] = 0.f;
     const float* vch = vc + (size_t)bh * nt * kD + t;
-#pragma unroll 8
-    for (int kt = 0; kt < nt; kt++) acc = __fadd_rn(acc, (float)(wexp[kt] * (double)vch[(size_t)kt * kD]));
-    coarse[((size_t)bh * nt + qt) * kD + t] = acc;
+    const int nq = min(kCoarseQT, nt - qt0);
+#pragma unroll 4
+    for (int kt = 0; kt < nt; kt++) {
+        const float v = vch[(size_t)kt * kD];
+#pragma unroll
+        for (int q = 0; q < kCoarseQT; q++)
+            if (q < nq) acc[q] = __fadd_rn(acc[q], __fmul_rn(wts[(size_t)q * nt + kt], v));
+    }
+#pragma unroll
+    for (int q = 0; q < kCoarseQT; q++)
+        if (q < nq) coarse[((size_t)bh * nt + qt0 + q) * kD + t] = acc[q];
 }
 
 // ------------------------------------------------------------------ 4. top-k tiles per query tile
@@ -186,6 +233,46 @@ __global__ void __launch_bounds__(256) vsa_topk_kernel(const float* __restrict__
         if (sel && pos < topk) out[pos] = (uint32_t)i;
         eq_seen += eq_tot;
         written += sel_tot;
+    }
+}
+
+// The same selection with one WARP per row (rows of up to kTopkWarpMax scores): no block-wide barriers.  grid
+// (ceil(rows / 8), 1), 256 threads; dynamic smem: 8 * nt keys.
+constexpr int kTopkWarpMax = 1024;
+__global__ void __launch_bounds__(256) vsa_topk_warp_kernel(const float* __restrict__ scores, int rows, int nt, int topk,
+                                                            uint32_t* __restrict__ selected) {
+    extern __shared__ uint32_t wkeys[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * 8 + warp;
+    if (row >= rows) return;  // warp-uniform; no block barrier below
+    uint32_t* keys = wkeys + (size_t)warp * nt;
+    const float* s = scores + (size_t)row * nt;
+    for (int i = lane; i < nt; i += 32) keys[i] = order_key(s[i]);
+    __syncwarp();
+    uint32_t T = 0u;
+    for (int b = 31; b >= 0; b--) {
+        const uint32_t cand = T | (1u << b);
+        int c = 0;
+        for (int i = lane; i < nt; i += 32) c += keys[i] >= cand;
+        if (__reduce_add_sync(0xffffffffu, c) >= topk) T = cand;
+    }
+    int c = 0;
+    for (int i = lane; i < nt; i += 32) c += keys[i] > T;
+    const int need_eq = topk - __reduce_add_sync(0xffffffffu, c);
+    uint32_t* out = selected + (size_t)row * topk;
+    int eq_seen = 0, written = 0;
+    const uint32_t below = (1u << lane) - 1u;
+    for (int base = 0; base < nt; base += 32) {
+        const int i = base + lane;
+        const uint32_t key = i < nt ? keys[i] : 0u;
+        const bool eq = i < nt && key == T;
+        const uint32_t eqm = __ballot_sync(0xffffffffu, eq);
+        const bool sel = i < nt && (key > T || (eq && eq_seen + __popc(eqm & below) < need_eq));
+        const uint32_t selm = __ballot_sync(0xffffffffu, sel);
+        const int pos = written + __popc(selm & below);
+        if (sel && pos < topk) out[pos] = (uint32_t)i;
+        eq_seen += __popc(eqm);
+        written += __popc(selm);
     }
 }
 
@@ -689,7 +776,7 @@ extern "C" int fv_vsa_forward_bf16(void* stream_, void* plan, const void* q, con
     fvrt::clear_error();
     Plan* pl = (Plan*)plan;
     if (!pl) return fvrt::fail(FV_ERR_INVALID, "vsa: null plan");
-    if (bh <= 0) return FV_DECLINED;
+    if (bh <= 0 || bh > 65535) return FV_DECLINED;  // bh rides in grid.y / grid.z of the small kernels
     if (pl->nt > 4096 || pl->nt >= (1 << 20)) return FV_DECLINED;  // the selection kernel keeps a row in shared memory
     int dev;
     int rc = fvrt::require_sm100(&dev);
@@ -714,12 +801,34 @@ extern "C" int fv_vsa_forward_bf16(void* stream_, void* plan, const void* q, con
     const float* qc = w.means;
     const float* kc = w.means + (size_t)bh * nt * fvvsa::kD;
     const float* vc = w.means + (size_t)2 * bh * nt * fvvsa::kD;
-    const int nb16 = (nt + 15) / 16;
-    fvvsa::vsa_scores_kernel<<<dim3(nb16, nb16, bh), 256, 0, stream>>>(qc, kc, nt, scale, w.scores);
+    {
+        static bool score_attr[64] = {};
+        if (!score_attr[dev]) {
+            FV_CUDA(cudaFuncSetAttribute(fvvsa::vsa_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fvvsa::kScoreSmem));
+            score_attr[dev] = true;
+        }
+        const int nb = (nt + fvvsa::kScoreTile - 1) / fvvsa::kScoreTile;
+        fvvsa::vsa_scores_kernel<<<dim3(nb, nb, bh), 256, fvvsa::kScoreSmem, stream>>>(qc, kc, nt, scale, w.scores);
+    }
     FV_CUDA(cudaGetLastError());
-    fvvsa::vsa_coarse_kernel<<<dim3(nt, bh), 128, (size_t)nt * sizeof(double), stream>>>(w.scores, vc, nt, w.coarse);
+    {
+        const size_t csm = (size_t)nt * sizeof(double) + (size_t)fvvsa::kCoarseQT * nt * sizeof(float);
+        static size_t coarse_attr[64] = {};
+        if (csm > 48 * 1024 && coarse_attr[dev] < csm) {
+            FV_CUDA(cudaFuncSetAttribute(fvvsa::vsa_coarse_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csm));
+            coarse_attr[dev] = csm;
+        }
+        fvvsa::vsa_coarse_kernel<<<dim3((nt + fvvsa::kCoarseQT - 1) / fvvsa::kCoarseQT, bh), 128, csm, stream>>>(w.scores, vc, nt,
+                                                                                                            w.coarse);
+    }
     FV_CUDA(cudaGetLastError());
-    fvvsa::vsa_topk_kernel<<<dim3(nt, bh), 256, (size_t)nt * sizeof(uint32_t), stream>>>(w.scores, nt, topk, w.selected);
+    if (nt <= fvvsa::kTopkWarpMax) {
+        const long long rows = (long long)bh * nt;
+        fvvsa::vsa_topk_warp_kernel<<<(unsigned)((rows + 7) / 8), 256, (size_t)8 * nt * sizeof(uint32_t), stream>>>(
+            w.scores, (int)rows, nt, topk, w.selected);
+    } else {
+        fvvsa::vsa_topk_kernel<<<dim3(nt, bh), 256, (size_t)nt * sizeof(uint32_t), stream>>>(w.scores, nt, topk, w.selected);
+    }
     FV_CUDA(cudaGetLastError());
 
     fvvsa::FineParams fp{};
