@@ -68,6 +68,7 @@ static EncodeTiledFn g_encode = nullptr;
 int encode_map4(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint64_t strides[3],
                 uint32_t box_rows) {
     if (!g_encode) {
+        std::lock_guard<std::mutex> lk(g_mu);
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
         FV_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));

@@ -4,6 +4,7 @@
 #include "fv_runtime.h"
 #include <math.h>
 #include <stdlib.h>
+#include <mutex>
 
 namespace fvsdpa {
 
@@ -159,9 +160,13 @@ static int launch(cudaStream_t stream, const void* q, const void* k, const void*
     const int var = chosen_variant();
     const bool masked = mask_mode != FV_MASK_NONE;
     const KernelFn fn = kernel_for(var, masked);
-    if (!attr_set[dev & 7][var][masked]) {
-        FV_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set[dev & 7][var][masked] = true;
+    {
+        static std::mutex attr_mu;
+        std::lock_guard<std::mutex> attr_lock(attr_mu);
+        if (!attr_set[dev & 7][var][masked]) {
+            FV_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set[dev & 7][var][masked] = true;
+        }
     }
     fn<<<(unsigned)grid, kThreads, smem, stream>>>(tq, tk, tv, p);
     FV_CUDA(cudaGetLastError());

@@ -31,7 +31,7 @@ class BlockCausal:
 _DENSE, _COMPOSED, _BLOCK_CAUSAL, _VDN_WINDOW, _KV_WINDOW = range(5)
 
 
-@dataclass(frozen=True)
+@dataclass(frozen=True, eq=False)
 class Plan:
     """What one attention call computes (rt/sdpa.rs:27-139)."""
     kind: int = _DENSE
