@@ -42,6 +42,11 @@ WORKLOADS = {
     "wan1p3b_480p_vsa": dict(batch=1, heads=12, grid=(21, 30, 52), block=0, vsa_topk=78,
                              desc="VSA block-sparse self-attention at the Wan-1.3B 480p grid: 624 tiles of 64 tokens, top-k 78 (12.5 %), "
                                   "sigmoid gate applied to seeded logits before the call"),
+    "wan1p3b_ar_kvwindow": dict(batch=1, heads=12, grid=(3, 30, 52), block=0, window=32760, rope_grid=(21, 30, 52),
+                                desc="causal (Self-Forcing) Wan-1.3B inference step: one block of 3 latent frames (4 680 rows) "
+                                     "against the cached 21-frame window (32 760 keys), Plan.kv_window; the step is prologue of the "
+                                     "block + write of its k/v into the cache tail + attention (keys cut in ranges when that fills "
+                                     "the SMs better; FV_SPLITKV=0 turns that off)"),
     "tiny": dict(batch=1, heads=12, grid=(3, 8, 8), block=0, desc="tiny Wan-arch dense self-attention (192 tokens)"),
 }
 def _metric_name():
@@ -134,13 +139,15 @@ def reference_arm(args, wl):
     dim = heads * 128
     hs = min(args.cpu_heads, heads)
     rows = np.sort(np.random.default_rng(0).choice(seq, size=min(args.cpu_rows, seq), replace=False)).astype(np.int32)
-    q, k, v = (O.bf16_round(O.seeded_normal(args.seed, 10 + i, (hs, seq, 128))) for i in range(3))
+    window = wl.get("window", 0)
+    keys = window or seq
+    q, k, v = (O.bf16_round(O.seeded_normal(args.seed, 10 + i, (hs, seq if i == 0 else keys, 128))) for i in range(3))
     causal = (block, 0, 0) if block else None
     ntok = min(args.cpu_tokens, seq)
     proj = O.bf16_round(O.seeded_normal(args.seed, 0, (1, ntok, 3 * dim)))
     w = np.ones(dim, np.float32)
     cos, sin = O.wan_rope(*grid)
-    cos, sin = cos[:ntok].copy(), sin[:ntok].copy()
+    cos, sin = cos[:ntok].copy(), sin[:ntok].copy()  # which positions the sample ropes does not change its cost
     t_attn, t_prep = [], []
     for i in range(args.warmup_cpu + args.steps_cpu):
         t0 = time.perf_counter()
@@ -157,9 +164,9 @@ def reference_arm(args, wl):
     if block:
         vis_rows = sum(min(seq, (int(r) // block + 1) * block) for r in rows)
     else:
-        vis_rows = len(rows) * seq
+        vis_rows = len(rows) * keys
     sample_flops = 4.0 * hs * vis_rows * 128
-    total_flops = 4.0 * batch * heads * visible_pairs(seq, block) * 128
+    total_flops = 4.0 * batch * heads * (float(seq) * window if window else visible_pairs(seq, block)) * 128
     full_seconds = ta * (total_flops / sample_flops) + tp * (batch * seq / ntok)
     return dict(value=total_flops / full_seconds / 1e12, seconds=ta + tp, cores=O.num_threads(), attn_tflops=sample_flops / ta / 1e12,
                 sample=f"attention: {len(rows)} of {seq} query rows x {hs} of {heads} heads x all keys ({sample_flops / 1e9:.1f} GFLOP in "
@@ -191,14 +198,20 @@ def main():
     seq = grid[0] * grid[1] * grid[2]
     dim = heads * 128
     total_flops = 4.0 * batch * heads * visible_pairs(seq, block) * 128
+    window = wl.get("window", 0)
+    if window:
+        total_flops = 4.0 * batch * heads * float(seq) * window * 128
     vsa_topk = wl.get("vsa_topk", 0)
     if vsa_topk:
         # the reference's count for the fine stage (padded slots, crates/fastvideo-gpucheck/src/kernels/vsa_dc.rs:648)
         # plus the coarse tile attention
         ntile = math.prod(-(-g // 4) for g in grid)
         total_flops = 4.0 * batch * heads * (ntile * 64.0) * (vsa_topk * 64.0) * 128 + 4.0 * batch * heads * ntile * ntile * 128
+    # inputs read by one step; below 4 x the 126 MB L2 the bench writes a flush buffer between steps
+    needs_flush = batch * seq * dim * 2 * 3 + 2 * batch * heads * window * 128 * 2 < 4 * 126e6
     cfg = dict(workload=f"{args.workload}: {wl['desc']}; b{batch} h{heads} S{seq} d128", seed=args.seed,
-               l2="inputs exceed L2 (no flush needed)" if batch * seq * dim * 2 * 3 > 2 * 126e6 else "L2 flushed between steps",
+               l2="inputs exceed L2 (no flush needed)" if not needs_flush else
+                  "L2 flushed between steps (512 MB written before each step, outside the per-step event pairs that are summed)",
                parallelism=f"sp{world}" if world > 1 else "single")
 
     if args.impl == "reference":
@@ -239,7 +252,9 @@ def main():
     proj = torch.randn((batch, length, 3 * dim), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
     wq = torch.ones(dim, device=dev)
     wk = torch.ones(dim, device=dev)
-    cos_all, sin_all = wan.wan_rope_tables_host(grid)
+    cos_all, sin_all = wan.wan_rope_tables_host(wl.get("rope_grid", grid))
+    if window:  # the block is the last frames of the window's grid
+        start = window - seq
     cos = torch.from_numpy(cos_all[start:start + length].copy()).to(dev)
     sin = torch.from_numpy(sin_all[start:start + length].copy()).to(dev)
     bh = batch * heads
@@ -248,6 +263,12 @@ def main():
         raise SystemExit("the chunk-causal workload is single-GPU in this bench")
     if vsa_topk and world > 1:
         raise SystemExit("the VSA workload is single-GPU in this bench")
+    if window and world > 1:
+        raise SystemExit("the KV-window workload is single-GPU in this bench")
+    k_cache = v_cache = None
+    if window:  # earlier blocks' keys and values, as the cache holds them: [b, h, window, 128] bf16
+        k_cache, v_cache = (torch.randn((batch, heads, window, 128), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+                            for _ in range(2))
     spa = sp.SpAttention(seq, bh, device=dev) if world > 1 else None
     vsa_in = None
     if vsa_topk:
@@ -260,6 +281,10 @@ def main():
         proj = vsa_in
     out_buf = torch.empty((bh, length, 128), dtype=torch.bfloat16, device=dev)
     launches_per_step = 5 if vsa_topk else (2 if world == 1 else 2 + spa.groups)
+    if window:  # prologue, attention, and the merge of the key ranges when the keys are cut
+        split = os.environ.get("FV_SPLITKV", "1") != "0" and sdpa.splitkv_choose(
+            bh, seq, window, torch.cuda.get_device_properties(dev).multi_processor_count) > 1
+        launches_per_step = 3 if split else 2
     attn_events = []
 
     def step(p, record=False):
@@ -277,7 +302,11 @@ def main():
         if record:
             e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
             e0.record()
-        if spa is not None:
+        if window:
+            k_cache[:, :, window - seq:].copy_(k.view(batch, heads, seq, 128))
+            v_cache[:, :, window - seq:].copy_(v.view(batch, heads, seq, 128))
+            o = sdpa.sdpa(q.view(batch, heads, seq, 128), k_cache, v_cache, sdpa.Plan.kv_window()).view(bh, seq, 128)
+        elif spa is not None:
             o = spa.forward(q, k, v, out=out_buf)
         else:
             o = sdpa.dense_fwd(q, k, v, causal=causal, out=out_buf)
@@ -301,12 +330,21 @@ def main():
     t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
     barrier()
     t0.record()
+    step_events = []
+    flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev) if needs_flush else None
     for _ in range(args.steps):
+        if needs_flush:
+            flush_buf.fill_(1)
+            s0 = torch.cuda.Event(enable_timing=True); s1 = torch.cuda.Event(enable_timing=True)
+            s0.record()
         step(proj, record=True)
+        if needs_flush:
+            s1.record()
+            step_events.append((s0, s1))
     t1.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
-    ms_total = t0.elapsed_time(t1)
+    ms_total = sum(a.elapsed_time(b) for a, b in step_events) if needs_flush else t0.elapsed_time(t1)
     attn_ms = sum(a.elapsed_time(b) for a, b in attn_events) / len(attn_events)
     assert sdpa.device_status() == 0
 
@@ -349,12 +387,14 @@ def main():
     # DRAM bytes per attention launch: measured on a smaller case of the same kernel (ncu dram__bytes_read.sum +
     # dram__bytes_write.sum of a 24-head x 8192-token capture: reads = 1.0007 x (Q + K + V), every output byte written
     # once) and scaled by the bytes of Q, K, V and O, which is what the traffic is proportional to.
-    traffic = None if vsa_topk else int(4 * bh * length * 128 * 2 * 1.0005) + (2 * bh * (seq - length) * 128 * 2 if world > 1 else 0)
+    traffic = None if (vsa_topk or window) else int(4 * bh * length * 128 * 2 * 1.0005) + (2 * bh * (seq - length) * 128 * 2 if world > 1 else 0)
     line = dict(metric=METRIC, value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
                 ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
                 config=cfg, value_note=UNIT_NOTE, per_gpu_tflops=value / world, frac_of_bf16_peak_burst=value / world / pk["burst"],
                 frac_of_bf16_peak_sustained=value / world / pk["sustained"], peaks=pk,
-                roofline=dict(bound="tensor", kernel="fv_vsa_fine_kernel (+4 small kernels in the timed span)" if vsa_topk else "fv_sdpa_fwd_d128",
+                roofline=dict(bound="tensor", kernel="fv_vsa_fine_kernel (+4 small kernels in the timed span)" if vsa_topk else
+                              ("fv_sdpa_fwd_d128 (+ cache-tail copies and fv_splitkv_merge_kernel in the timed span)" if window
+                               else "fv_sdpa_fwd_d128"),
                               achieved=achieved, peak=pk["sustained"], unit="TFLOP/s",
                               frac=achieved / pk["sustained"], frac_of_burst=achieved / pk["burst"], of=pk["source"],
                               ms_per_launch_set=attn_ms, traffic=traffic,

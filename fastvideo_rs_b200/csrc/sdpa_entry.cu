@@ -140,13 +140,21 @@ extern "C" void fv_shard_ranges(int seq, int world, int* start, int* len) {
 }
 
 // The Mma step: this library's kernel when the rule picks it, else not ours.
+// With a workspace, an unmasked call whose grid fills the SMs a ragged number of times is cut along the keys.
 static int run_mma(void* stream, const void* q, const void* k, const void* v, const Shape& sh, bool out_bf16,
-                   const Probe& p, float scale, void* out, int mask_mode, int bt, int win, int sink) {
+                   const Probe& p, float scale, void* out, int mask_mode, int bt, int win, int sink,
+                   void* ws = nullptr, size_t ws_bytes = 0) {
     const MmaKernel m = mma_kernel(sh, out_bf16, p);
     if (m.kind != MmaKind::Fixed || m.kernel != FlashKernel::B200) return FV_DECLINED;
     if (!sh.has_dims) return FV_DECLINED;
     const Dims& d = sh.dims;
     if (!mma_sdpa_supported(d.b, d.h, d.sq, d.sk, d.d, p.has_sm ? p.sm_major : 0)) return FV_DECLINED;
+    if (ws && mask_mode == FV_MASK_NONE && d.d == 128 && d.sq <= 0x3fffffff && d.sk <= 0x3fffffff) {
+        const int splits = fv_sdpa_splitkv_choose((int)(d.b * d.h), (int)d.sq, (int)d.sk, (int)p.sms);
+        if (splits > 1 && fv_sdpa_splitkv_workspace_bytes((int)(d.b * d.h), (int)d.sq, splits) <= ws_bytes)
+            return fv_sdpa_splitkv_bf16(stream, q, k, v, out, out_bf16 ? 1 : 0, (int)(d.b * d.h), (int)d.sq, (int)d.sk,
+                                        (int)d.d, scale, splits, 0, ws, ws_bytes);
+    }
     return fv_sdpa_dense_bf16(stream, q, k, v, out, out_bf16 ? 1 : 0, (int)(d.b * d.h), (int)d.sq, (int)d.sk, (int)d.d,
                               scale, mask_mode, bt, win, sink, 0);
 }
@@ -154,6 +162,27 @@ static int run_mma(void* stream, const void* q, const void* k, const void* v, co
 extern "C" int fv_sdpa(void* stream, const void* q, const void* k, const void* v, const size_t q_shape[4],
                        const size_t k_shape[4], const size_t v_shape[4], const fv_plan* plan, const fv_probe* probe,
                        void* out, int out_is_bf16) {
+    return fv_sdpa_ws(stream, q, k, v, q_shape, k_shape, v_shape, plan, probe, out, out_is_bf16, nullptr, 0);
+}
+
+extern "C" size_t fv_sdpa_ws_bytes(const size_t q_shape[4], const size_t k_shape[4], const fv_plan* plan,
+                                   const fv_probe* probe) {
+    if (!q_shape || !k_shape || !plan) return 0;
+    if (plan->kind != FV_PLAN_KV_WINDOW && !(plan->kind == FV_PLAN_DENSE && !plan->has_mask)) return 0;
+    fv_probe live;
+    if (!probe) {
+        fv_probe_live(&live);
+        probe = &live;
+    }
+    const size_t bh = q_shape[0] * q_shape[1];
+    if (q_shape[3] != 128 || bh == 0 || bh > 65535 || q_shape[2] > 0x3fffffff || k_shape[2] > 0x3fffffff) return 0;
+    const int splits = fv_sdpa_splitkv_choose((int)bh, (int)q_shape[2], (int)k_shape[2], probe->sms);
+    return splits > 1 ? fv_sdpa_splitkv_workspace_bytes((int)bh, (int)q_shape[2], splits) : 0;
+}
+
+extern "C" int fv_sdpa_ws(void* stream, const void* q, const void* k, const void* v, const size_t q_shape[4],
+                          const size_t k_shape[4], const size_t v_shape[4], const fv_plan* plan, const fv_probe* probe,
+                          void* out, int out_is_bf16, void* workspace, size_t workspace_bytes) {
     fvrt::clear_error();
     if (!q_shape || !k_shape || !v_shape || !plan) return fvrt::fail(FV_ERR_INVALID, "sdpa expects BHSD");
     fv_probe live;
@@ -175,7 +204,8 @@ extern "C" int fv_sdpa(void* stream, const void* q, const void* k, const void* v
                     return fvrt::fail(FV_ERR_INVALID, "FASTVIDEO_SDPA=%s is retired: unset FASTVIDEO_SDPA for dense attention",
                                       st.retired == Backend::Sparse ? "sparse" : "host");
                 if (st.kind != StepKind::Mma) return FV_DECLINED;  // an earlier step of the route is the caller's
-                const int rc = run_mma(stream, q, k, v, sh, st.out_bf16 != 0, p, scale, out, FV_MASK_NONE, 0, 0, 0);
+                const int rc = run_mma(stream, q, k, v, sh, st.out_bf16 != 0, p, scale, out, FV_MASK_NONE, 0, 0, 0,
+                                       plan->has_mask ? nullptr : workspace, workspace_bytes);
                 return rc;  // ran, declined (caller continues with the next step), or error
             }
             return FV_DECLINED;
@@ -201,7 +231,8 @@ extern "C" int fv_sdpa(void* stream, const void* q, const void* k, const void* v
             for (const Step& st : route) {
                 if (st.kind == StepKind::Retired) return fvrt::fail(FV_ERR_INVALID, "FASTVIDEO_SDPA backend is retired");
                 if (st.kind != StepKind::Mma) return FV_DECLINED;
-                return run_mma(stream, q, k, v, sh, st.out_bf16 != 0, p, 1.0f / sqrtf(d), out, FV_MASK_NONE, 0, 0, 0);
+                return run_mma(stream, q, k, v, sh, st.out_bf16 != 0, p, 1.0f / sqrtf(d), out, FV_MASK_NONE, 0, 0, 0,
+                               workspace, workspace_bytes);
             }
             return FV_DECLINED;
         }

@@ -2,6 +2,7 @@
 #include "sdpa_fwd.cuh"
 #include "sdpa_fwd64.cuh"
 #include "fv_runtime.h"
+#include <cuda_bf16.h>
 #include <math.h>
 #include <stdlib.h>
 #include <mutex>
@@ -85,7 +86,7 @@ static int chosen_variant() {
 static int launch(cudaStream_t stream, const void* q, const void* k, const void* v, void* out, int out_is_bf16, int bh,
                   int sq, int nseg, const int* seg_len, const int* seg_start, int seg_rows, float scale, int mask_mode,
                   int block_tokens, int window, int sink, int q_row0, float* lse_out, const float* prev_o,
-                  const float* prev_lse, int* status_in = nullptr, int out_heads = 0) {
+                  const float* prev_lse, int* status_in = nullptr, int out_heads = 0, int q_div = 1) {
     int dev;
     int rc = fvrt::require_sm100(&dev);
     if (rc != FV_RAN) return rc;
@@ -101,6 +102,7 @@ static int launch(cudaStream_t stream, const void* q, const void* k, const void*
     if (mask_mode == FV_MASK_BLOCK_CAUSAL && (block_tokens < 1 || window < 0 || sink < 0 || q_row0 < 0))
         return fvrt::fail(FV_ERR_INVALID, "sdpa: block-causal needs block_tokens >= 1, window, sink, q_row0 >= 0");
     if (nseg < 1 || nseg > kMaxSeg) return fvrt::fail(FV_ERR_INVALID, "sdpa: 1..%d K/V segments", kMaxSeg);
+    if (q_div < 1 || bh % q_div != 0) return fvrt::fail(FV_ERR_INVALID, "sdpa: %d planes do not split by %d", bh, q_div);
 
     Params p{};
     p.out = out;
@@ -131,6 +133,7 @@ static int launch(cudaStream_t stream, const void* q, const void* k, const void*
     p.sink = sink;
     p.q_row0 = q_row0;
     p.heavy_first = mask_mode == FV_MASK_BLOCK_CAUSAL;
+    p.q_div = q_div;
     if (status_in) {
         p.status = status_in;
     } else {
@@ -143,8 +146,9 @@ static int launch(cudaStream_t stream, const void* q, const void* k, const void*
 
     CUtensorMap tq, tk, tv;
     {
-        const uint64_t dq[4] = {128, (uint64_t)sq, (uint64_t)bh, 1};
-        const uint64_t sqb[3] = {256, (uint64_t)sq * 256, (uint64_t)sq * 256 * bh};
+        const uint64_t qplanes = (uint64_t)(bh / q_div);
+        const uint64_t dq[4] = {128, (uint64_t)sq, qplanes, 1};
+        const uint64_t sqb[3] = {256, (uint64_t)sq * 256, (uint64_t)sq * 256 * qplanes};
         rc = fvrt::encode_map4(&tq, q, dq, sqb, 128);
         if (rc != FV_RAN) return rc;
         const uint64_t dk[4] = {128, (uint64_t)seg_rows, (uint64_t)bh, (uint64_t)nseg};
@@ -160,6 +164,7 @@ static int launch(cudaStream_t stream, const void* q, const void* k, const void*
     const int var = chosen_variant();
     const bool masked = mask_mode != FV_MASK_NONE;
     const KernelFn fn = kernel_for(var, masked);
+    if (q_div > 1 && (var == 100 || var == 101)) return FV_DECLINED;  // the 64-key schedule has no split-KV form
     {
         static std::mutex attr_mu;
         std::lock_guard<std::mutex> attr_lock(attr_mu);
@@ -225,6 +230,120 @@ static int two_pass_noalloc(cudaStream_t stream, const void* q, const void* k_lo
                   FV_MASK_NONE, 0, 0, 0, 0, nullptr, o1, lse1, status);
 }
 
+
+// ---- split-KV: few query rows against a long key window ----------------------------------------------
+// A block of 4 680 queries over a 32 760-key window fills 148 SMs 1.54 times: the second wave runs
+// half empty.  Each head's keys are cut into `splits` equal ranges that run as planes of their own
+// (k and v are only viewed as [bh * splits, sk / splits, 128]; q is read through q_div), every plane
+// leaves a normalised f32 result and its log-sum-exp in the workspace, and one HBM-bound kernel merges
+// them.  The merge is the two-pass formula of the epilogue applied to `splits` parts at once.
+constexpr int kMaxSplits = 8;
+
+template <int OUT16>
+__global__ void __launch_bounds__(256)
+fv_splitkv_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, void* __restrict__ out,
+                        int bh, int sq, int splits, int out_heads) {
+    const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);  // one warp per (plane, query row)
+    if (row >= (long long)bh * sq) return;
+    const int lane = threadIdx.x & 31;
+    const int h = (int)(row / sq), r = (int)(row % sq);
+    float lse[kMaxSplits];
+    float M = __int_as_float(0xff800000);
+#pragma unroll
+    for (int s = 0; s < kMaxSplits; s++) {
+        lse[s] = s < splits ? part_lse[((size_t)h * splits + s) * sq + r] : __int_as_float(0xff800000);
+        M = fmaxf(M, lse[s]);
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (M != __int_as_float(0xff800000)) {
+        float den = 0.f;
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; s++) {
+            lse[s] = s < splits ? exp2f(lse[s] - M) : 0.f;  // now the weight of part s
+            den += lse[s];
+        }
+        const float inv = 1.f / den;
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; s++) {
+            if (s >= splits) break;
+            const float w = lse[s] * inv;
+            const float4 t = reinterpret_cast<const float4*>(part_o + (((size_t)h * splits + s) * sq + r) * kD)[lane];
+            acc.x = fmaf(t.x, w, acc.x);
+            acc.y = fmaf(t.y, w, acc.y);
+            acc.z = fmaf(t.z, w, acc.z);
+            acc.w = fmaf(t.w, w, acc.w);
+        }
+    }
+    size_t ooff = (size_t)row * kD;
+    if (out_heads > 0) ooff = (((size_t)(h / out_heads) * sq + r) * out_heads + h % out_heads) * kD;
+    if (OUT16) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        reinterpret_cast<uint2*>(reinterpret_cast<unsigned short*>(out) + ooff)[lane] =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    } else {
+        reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + ooff)[lane] = acc;
+    }
+}
+
+static size_t splitkv_bytes(long long bh, long long sq, int splits) {
+    return (size_t)bh * splits * sq * (kD + 1) * sizeof(float);
+}
+
+// Estimated duration in microseconds of `splits` ranges on `sms` SMs: equal CTAs run in whole waves, a
+// 256 x 128 tile step takes about 2 us, a CTA pays about 3 steps of fill and drain (4 with the f32
+// store of a part), the merge moves (splits + 1) x the output at about 5 TB/s.
+static double splitkv_cost(long long bh, long long sq, long long sk, int splits, int sms) {
+    const long long nqb = (sq + kRowsPerCta - 1) / kRowsPerCta;
+    const long long waves = (nqb * bh * splits + sms - 1) / sms;
+    const long long tiles = (sk / splits + kBN - 1) / kBN;
+    double us = (double)waves * (double)(tiles + (splits > 1 ? 4 : 3)) * 2.0;
+    if (splits > 1) us += 3.0 + (double)bh * sq * kD * 4.0 * (splits + 1) / 5.0e6;
+    return us;
+}
+
+static int splitkv_choose(long long bh, long long sq, long long sk, int sms) {
+    if (bh <= 0 || sq <= 0 || sk <= 0 || sms <= 0) return 1;
+    int best = 1;
+    double best_us = splitkv_cost(bh, sq, sk, 1, sms);
+    for (int s = 2; s <= kMaxSplits; s++) {
+        if (sk % s != 0 || sk / s < 4 * kBN || bh * s > 0x7fffffffll) continue;
+        const double us = splitkv_cost(bh, sq, sk, s, sms);
+        if (us < 0.97 * best_us) {  // a split has to pay for itself by more than the model's noise
+            best = s;
+            best_us = us;
+        }
+    }
+    return best;
+}
+
+static int splitkv(cudaStream_t stream, const void* q, const void* k, const void* v, void* out, int out_is_bf16, int bh,
+                   int sq, int sk, float scale, int splits, int out_heads, void* workspace, size_t workspace_bytes) {
+    if (splits < 2 || splits > kMaxSplits) return fvrt::fail(FV_ERR_INVALID, "split-KV: 2..%d splits", kMaxSplits);
+    if (sk % splits != 0) return fvrt::fail(FV_ERR_INVALID, "split-KV: %d keys do not divide into %d ranges", sk, splits);
+    if ((long long)bh * splits > 0x7fffffffll) return FV_DECLINED;
+    if (out_heads < 0 || (out_heads > 0 && bh % out_heads != 0))
+        return fvrt::fail(FV_ERR_INVALID, "split-KV: %d planes are not whole batches of %d heads", bh, out_heads);
+    const size_t need = splitkv_bytes(bh, sq, splits);
+    if (!workspace || workspace_bytes < need)
+        return fvrt::fail(FV_ERR_INVALID, "split-KV: workspace of %zu bytes, %zu needed", workspace_bytes, need);
+    if (((uintptr_t)workspace | (uintptr_t)out) & 15) return fvrt::fail(FV_ERR_INVALID, "split-KV: buffers must be 16-byte aligned");
+    float* part_o = static_cast<float*>(workspace);
+    float* part_lse = part_o + (size_t)bh * splits * sq * kD;
+    const int len = sk / splits, start = 0;
+    // The key index only matters under a mask; split-KV is unmasked, so every range may start at 0.
+    int rc = launch(stream, q, k, v, part_o, 0, bh * splits, sq, 1, &len, &start, len, scale, FV_MASK_NONE, 0, 0, 0, 0,
+                    part_lse, nullptr, nullptr, nullptr, 0, splits);
+    if (rc != FV_RAN) return rc;
+    const long long rows = (long long)bh * sq;
+    const unsigned grid = (unsigned)((rows + 7) / 8);
+    if (out_is_bf16)
+        fv_splitkv_merge_kernel<1><<<grid, 256, 0, stream>>>(part_o, part_lse, out, bh, sq, splits, out_heads);
+    else
+        fv_splitkv_merge_kernel<0><<<grid, 256, 0, stream>>>(part_o, part_lse, out, bh, sq, splits, out_heads);
+    FV_CUDA(cudaGetLastError());
+    return FV_RAN;
+}
+
 }  // namespace fvsdpa
 
 extern "C" int fv_sdpa_two_pass_noalloc_bf16(void* stream, const void* q, const void* k_local, const void* v_local,
@@ -273,4 +392,23 @@ extern "C" int fv_sdpa_dense_merged_bf16(void* stream, const void* q, const void
     const int len = sk, start = 0;
     return fvsdpa::launch((cudaStream_t)stream, q, k, v, out, out_is_bf16, batch * heads, sq, 1, &len, &start, sk, scale,
                           mask_mode, block_tokens, window, sink, q_row0, nullptr, nullptr, nullptr, nullptr, heads);
+}
+
+extern "C" int fv_sdpa_splitkv_choose(int bh, int sq, int sk, int sm_count) {
+    return fvsdpa::splitkv_choose(bh, sq, sk, sm_count);
+}
+
+extern "C" size_t fv_sdpa_splitkv_workspace_bytes(int bh, int sq, int splits) {
+    if (bh <= 0 || sq <= 0 || splits < 2 || splits > fvsdpa::kMaxSplits) return 0;
+    return fvsdpa::splitkv_bytes(bh, sq, splits);
+}
+
+extern "C" int fv_sdpa_splitkv_bf16(void* stream, const void* q, const void* k, const void* v, void* out,
+                                    int out_is_bf16, int bh, int sq, int sk, int d, float scale, int splits,
+                                    int out_heads, void* workspace, size_t workspace_bytes) {
+    fvrt::clear_error();
+    if (d != 128 || bh <= 0 || sq <= 0 || sk <= 0) return FV_DECLINED;
+    if (sq > 0x3fffffff || sk > 0x3fffffff) return FV_DECLINED;
+    return fvsdpa::splitkv((cudaStream_t)stream, q, k, v, out, out_is_bf16, bh, sq, sk, scale, splits, out_heads,
+                           workspace, workspace_bytes);
 }

@@ -60,6 +60,7 @@ struct Params {
     int block_tokens, window, sink;
     int q_row0;              // global index of query row 0 (sequence-parallel shard offset)
     int heavy_first;         // walk query blocks from the last to the first
+    int q_div;               // > 1: split-KV, plane i of k/v/out reads plane i / q_div of q
 };
 
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL) || !defined(__CUDA_ARCH__)
@@ -572,10 +573,11 @@ FV_DEV void sdpa_body(const CUtensorMap* tq, const CUtensorMap* tk, const CUtens
             tma_prefetch_desc(tk);
             tma_prefetch_desc(tv);
             mbar_expect_tx(b_q, 2 * kTileB);
-            tma_load4(sQ, tq, b_q, 0, q0, bh, 0);
-            tma_load4(sQ + kPanelB, tq, b_q, 64, q0, bh, 0);
-            tma_load4(sQ + kTileB, tq, b_q, 0, q0 + 128, bh, 0);
-            tma_load4(sQ + kTileB + kPanelB, tq, b_q, 64, q0 + 128, bh, 0);
+            const int bhq = p.q_div > 1 ? bh / p.q_div : bh;
+            tma_load4(sQ, tq, b_q, 0, q0, bhq, 0);
+            tma_load4(sQ + kPanelB, tq, b_q, 64, q0, bhq, 0);
+            tma_load4(sQ + kTileB, tq, b_q, 0, q0 + 128, bhq, 0);
+            tma_load4(sQ + kTileB + kPanelB, tq, b_q, 64, q0 + 128, bhq, 0);
             int idx = 0;
             bool ok = true;
             walk_tiles<MASKED>(p, vis_lo, vis_hi, vis_sink, [&](int seg, int t, int, int) -> bool {

@@ -5,6 +5,7 @@ sdpa_rule's choice; when that choice is not this library's sm_100a kernel the ca
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -104,15 +105,23 @@ def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, plan: Plan, *, out_b
         raise ValueError("sdpa expects BHSD")
     for n, t in (("q", q), ("k", k), ("v", v)):
         _check_bf16_cuda(n, t)
-    out = torch.empty(q.shape, dtype=torch.bfloat16 if out_bf16 else torch.float32, device=q.device)
     cs4 = ctypes.c_size_t * 4
     pc = plan.to_c()
     pr = probe.to_c() if probe is not None else None
+    out = torch.empty(q.shape, dtype=torch.bfloat16 if out_bf16 else torch.float32, device=q.device)
+    L = _lib.lib()
+    prp = ctypes.byref(pr) if pr is not None else None
     with torch.cuda.device(q.device):
-        rc = _lib.lib().fv_sdpa(_stream_ptr(), ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()),
-                                ctypes.c_void_p(v.data_ptr()), cs4(*q.shape), cs4(*k.shape), cs4(*v.shape),
-                                ctypes.byref(pc), ctypes.byref(pr) if pr is not None else None,
-                                ctypes.c_void_p(out.data_ptr()), int(out_bf16))
+        # A short query block against a long window is cut along the keys when that fills the SMs better.
+        L.fv_sdpa_ws_bytes.restype = ctypes.c_size_t
+        need = int(L.fv_sdpa_ws_bytes(cs4(*q.shape), cs4(*k.shape), ctypes.byref(pc), prp)) \
+            if os.environ.get("FV_SPLITKV", "1") != "0" else 0
+        ws = _workspace(q.device, need) if need else None
+        rc = L.fv_sdpa_ws(_stream_ptr(), ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()),
+                          ctypes.c_void_p(v.data_ptr()), cs4(*q.shape), cs4(*k.shape), cs4(*v.shape),
+                          ctypes.byref(pc), prp, ctypes.c_void_p(out.data_ptr()), int(out_bf16),
+                          ctypes.c_void_p(ws.data_ptr() if ws is not None else None),
+                          ctypes.c_size_t(ws.numel() if ws is not None else 0))
     _lib.check(rc, "sdpa")
     return out
 
@@ -159,6 +168,55 @@ def dense_fwd_merged(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale
                                                   ctypes.c_void_p(v.data_ptr()), ctypes.c_void_p(out.data_ptr()), int(out_bf16),
                                                   b, h, sq, sk, d, ctypes.c_float(scale), mode, bt, win, sink, 0)
     _lib.check(rc, "dense_fwd_merged")
+    return out
+
+
+_split_ws: dict = {}  # device index -> workspace tensor, grown on demand
+
+
+def _workspace(device: torch.device, need: int) -> torch.Tensor:
+    """One split-KV workspace per device, reused by every call on it (calls on one device share its stream
+    order; a caller with several streams passes workspaces of its own to splitkv_fwd)."""
+    ws = _split_ws.get(device.index)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device=device)
+        _split_ws[device.index] = ws
+    return ws
+
+
+def splitkv_choose(bh: int, sq: int, sk: int, sm_count: int) -> int:
+    """How many key ranges the cost model cuts this shape into on a GPU of `sm_count` SMs (1 = no split)."""
+    return int(_lib.lib().fv_sdpa_splitkv_choose(bh, sq, sk, sm_count))
+
+
+def splitkv_workspace_bytes(bh: int, sq: int, splits: int) -> int:
+    L = _lib.lib()
+    L.fv_sdpa_splitkv_workspace_bytes.restype = ctypes.c_size_t
+    return int(L.fv_sdpa_splitkv_workspace_bytes(bh, sq, splits))
+
+
+def splitkv_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, splits: int, *, scale: Optional[float] = None,
+                out_bf16: bool = True, out_heads: int = 0, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Unmasked attention of a short query block over a long key window (Plan::kv_window, rt/sdpa.rs:122-133) with
+    each head's keys cut into `splits` ranges that run side by side: q [bh, sq, 128], k / v [bh, sk, 128] ->
+    [bh, sq, 128], or [bh / out_heads, sq, out_heads * 128] with out_heads > 0."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _check_bf16_cuda(n, t)
+    bh, sq, d = q.shape
+    sk = k.shape[1]
+    if k.shape != (bh, sk, d) or v.shape != k.shape:
+        raise ValueError("splitkv_fwd: k and v must be [bh, sk, d] of q")
+    scale = float(scale) if scale is not None else 1.0 / d ** 0.5
+    if workspace is None:
+        workspace = _workspace(q.device, splitkv_workspace_bytes(bh, sq, splits))
+    shape = (bh // out_heads, sq, out_heads * d) if out_heads > 0 else (bh, sq, d)
+    out = torch.empty(shape, dtype=torch.bfloat16 if out_bf16 else torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().fv_sdpa_splitkv_bf16(_stream_ptr(), ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()),
+                                             ctypes.c_void_p(v.data_ptr()), ctypes.c_void_p(out.data_ptr()), int(out_bf16),
+                                             bh, sq, sk, d, ctypes.c_float(scale), int(splits), int(out_heads),
+                                             ctypes.c_void_p(workspace.data_ptr()), ctypes.c_size_t(workspace.numel()))
+    _lib.check(rc, "splitkv_fwd")
     return out
 
 

@@ -83,6 +83,26 @@ FV_API int fv_sdpa_dense_merged_bf16(void* stream, const void* q, const void* k,
                                      int out_is_bf16, int batch, int heads, int sq, int sk, int d, float scale,
                                      int mask_mode, int block_tokens, int window, int sink, int q_row0);
 
+/* ---- split-KV: a short query block against a long key window ----------------------
+ * The shape of Plan::kv_window (crates/fastvideo-cudarc/src/rt/sdpa.rs:122-133, :300-326): the causal Wan caller
+ * (crates/fastvideo-cudarc/src/wan/transformer.rs:250-313, wan/causal.rs) attends one block of frames (e.g. 4 680
+ * rows) to the cached window (up to 32 760 keys), unmasked.  Such a launch fills the GPU a non-integer number of
+ * times; cutting each head's keys into `splits` equal ranges that run side by side and merging the parts by their
+ * log-sum-exp evens that out.  Same result as fv_sdpa_dense_bf16 up to f32 rounding of the merge.
+ *
+ * fv_sdpa_splitkv_choose: the number of ranges (1 = do not split, else 2..8, always a divisor of sk) a cost model
+ *   picks for this shape on a GPU with sm_count SMs.
+ * fv_sdpa_splitkv_workspace_bytes: bytes of caller-owned device workspace for `splits` ranges (0 for bad arguments).
+ * fv_sdpa_splitkv_bf16: q [bh, sq, 128], k and v [bh, sk, 128] bf16; out [bh, sq, 128], or with out_heads = h > 0
+ *   the merged-heads layout [bh / h, sq, h * 128]; bf16 or f32.  splits in 2..8 with sk % splits == 0 (else an
+ *   error).  Launches the attention kernel once over bh * splits planes and one merge kernel; nothing synchronises.
+ */
+FV_API int fv_sdpa_splitkv_choose(int bh, int sq, int sk, int sm_count);
+FV_API size_t fv_sdpa_splitkv_workspace_bytes(int bh, int sq, int splits);
+FV_API int fv_sdpa_splitkv_bf16(void* stream, const void* q, const void* k, const void* v, void* out, int out_is_bf16,
+                                int bh, int sq, int sk, int d, float scale, int splits, int out_heads, void* workspace,
+                                size_t workspace_bytes);
+
 /* The general form behind fv_sdpa_dense_bf16, used by the sequence-parallel path.
  * K and V are `nseg` segments (nseg <= FV_MAX_SEGMENTS), segment s holding seg_len[s]
  * keys whose global indices start at seg_start[s]; segment s of head h starts at element
@@ -298,6 +318,17 @@ typedef struct fv_plan {
 FV_API int fv_sdpa(void* stream, const void* q, const void* k, const void* v, const size_t q_shape[4],
                    const size_t k_shape[4], const size_t v_shape[4], const fv_plan* plan, const fv_probe* probe,
                    void* out, int out_is_bf16);
+
+/* fv_sdpa with a caller-owned device workspace.  fv_sdpa_ws_bytes gives the size this shape can use (0: none --
+ * the call is then fv_sdpa).  With at least that many bytes, an unmasked plan (Plan::kv_window above all: a block of
+ * frames against the cached window, crates/fastvideo-cudarc/src/wan/transformer.rs:250-313) whose grid would fill
+ * the SMs a ragged number of times runs as fv_sdpa_splitkv_bf16.  A null or smaller workspace is not an error: the
+ * call runs unsplit. */
+FV_API size_t fv_sdpa_ws_bytes(const size_t q_shape[4], const size_t k_shape[4], const fv_plan* plan,
+                               const fv_probe* probe);
+FV_API int fv_sdpa_ws(void* stream, const void* q, const void* k, const void* v, const size_t q_shape[4],
+                      const size_t k_shape[4], const size_t v_shape[4], const fv_plan* plan, const fv_probe* probe,
+                      void* out, int out_is_bf16, void* workspace, size_t workspace_bytes);
 
 /* ---- sequence-parallel split ------------------------------------------------------------
  * sp::shard_ranges (crates/fastvideo-cudarc/src/rt/sp.rs:16-28): contiguous shards, the
