@@ -88,7 +88,21 @@ FV_DEV void tma_load4(uint32_t dst, const void* map, uint32_t bar, int c0, int c
         : "memory");
 }
 
-// ------------------------------------------------------------------- tcgen05
+// 1-D bulk copy global -> shared, completion on an mbarrier.  Both addresses and the size are multiples of 16 bytes.
+FV_DEV void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// Bounded wait that ignores the abort flag: the exit path uses it to let copies in flight land.
+FV_DEV bool mbar_drain(uint32_t bar, uint32_t parity) {
+    const long long t0 = clock64();
+    while (!mbar_try(bar, parity)) {
+        if (clock64() - t0 > FV_WAIT_CYCLES) return false;
+    }
+    return true;
+}
+
 FV_DEV void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 FV_DEV void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 

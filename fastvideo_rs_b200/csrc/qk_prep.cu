@@ -10,9 +10,11 @@
 // y = (x*inv)*w, even = y0*cos[s,even] - y1*sin[s,even+1], odd = y0*sin[s,even+1] + y1*cos[s,even],
 // every product and sum rounded separately (no fused multiply-add), then one rounding to bf16.
 // Only the order of the sum of squares differs (tree reduction instead of a sequential sum).
+#include "fv_ptx.cuh"
 #include "fv_runtime.h"
 #include <cuda_bf16.h>
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 #include <vector>
 
@@ -150,6 +152,191 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_kernel(const Params
     if (p.k_out) finish(xk, sk, wkv, p.k_out);
 }
 
+
+// ---- the same arithmetic behind a ring of staged rows -----------------------------------------------
+// One CTA per row pays the whole DRAM round trip once per row with nothing else in flight.  Here a
+// CTA is persistent: it walks rows blockIdx.x, + gridDim.x, ... and keeps `stages` of them in flight
+// as bulk copies (q, k, v column ranges of the projection row and the row's cos / sin) into a ring
+// in shared memory, each stage completing on an mbarrier.  The block reduction's barrier doubles as
+// "every thread has read its part of the stage", after which one thread refills it.  The norm
+// weights stay in registers for the CTA's lifetime.  Values and rounding are those of the kernel
+// above, bit for bit (same reduction tree).
+struct RingGeom {
+    int stages;
+    uint32_t off_k, off_v, off_cos, off_sin;  // byte offsets inside a stage (q at 0)
+    uint32_t stage_bytes;
+    long long rows;                            // batch * seq
+    int* status;
+};
+
+template <int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_ring_kernel(const Params p, const RingGeom g) {
+    using namespace fvp;
+    extern __shared__ __align__(128) unsigned char ring_smem[];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = blockDim.x >> 5;
+    const bool act = t < p.heads * 16;
+    const int h = act ? (8 * t) / kD : 0, pd = act ? (8 * t) % kD : 0;
+    const uint32_t dimB = (uint32_t)p.heads * kD * 2u;
+    const uint32_t base = smem_u32(ring_smem);
+    const uint32_t bars = base + (uint32_t)g.stages * g.stage_bytes;
+    unsigned char* tail = ring_smem + (size_t)g.stages * g.stage_bytes + 8 * g.stages;
+    float* red = reinterpret_cast<float*>(tail);                       // [2][2 * nwarps]
+    volatile int* abort_ptr = reinterpret_cast<volatile int*>(tail + 16 * nwarps);
+
+    if (t == 0) {
+        for (int s = 0; s < g.stages; s++) mbar_init(bars + 8 * s, 1);
+        *abort_ptr = (*(volatile int*)g.status != FV_ST_OK) ? 1 : 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+    if (*abort_ptr) return;  // CTA-uniform
+    const WaitCtl ctl{abort_ptr, g.status, 7};
+
+    uint32_t row_bytes = 0;
+    if (p.q_out) row_bytes += dimB;
+    if (p.k_out) row_bytes += dimB;
+    if (p.v_out) row_bytes += dimB;
+    if (p.cosv) row_bytes += 2u * kD * 4u;
+    auto issue = [&](long long row, int s) {  // one thread
+        const uint32_t dst = base + (uint32_t)s * g.stage_bytes, bar = bars + 8 * s;
+        const __nv_bfloat16* src = p.proj + (size_t)row * p.width;
+        mbar_expect_tx(bar, row_bytes);
+        if (p.q_out) bulk_load(dst, src + p.col_q, dimB, bar);
+        if (p.k_out) bulk_load(dst + g.off_k, src + p.col_k, dimB, bar);
+        if (p.v_out) bulk_load(dst + g.off_v, src + p.col_v, dimB, bar);
+        if (p.cosv) {
+            const size_t sidx = (size_t)(row % p.seq) * kD;
+            bulk_load(dst + g.off_cos, p.cosv + sidx, kD * 4u, bar);
+            bulk_load(dst + g.off_sin, p.sinv + sidx, kD * 4u, bar);
+        }
+    };
+    long long issued = 0;  // rows of this CTA handed to the copy unit (thread 0 only)
+    if (t == 0) {
+        for (int s = 0; s < g.stages; s++) {
+            const long long row = (long long)blockIdx.x + issued * gridDim.x;
+            if (row >= g.rows) break;
+            issue(row, s);
+            issued++;
+        }
+    }
+
+    float wqv[8], wkv[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) wqv[i] = wkv[i] = 0.f;
+    if (act && p.q_out) {
+        const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.wq + 8 * t)), w1 = __ldg(reinterpret_cast<const float4*>(p.wq + 8 * t + 4));
+        wqv[0] = w0.x; wqv[1] = w0.y; wqv[2] = w0.z; wqv[3] = w0.w; wqv[4] = w1.x; wqv[5] = w1.y; wqv[6] = w1.z; wqv[7] = w1.w;
+    }
+    if (act && p.k_out) {
+        const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.wk + 8 * t)), w1 = __ldg(reinterpret_cast<const float4*>(p.wk + 8 * t + 4));
+        wkv[0] = w0.x; wkv[1] = w0.y; wkv[2] = w0.z; wkv[3] = w0.w; wkv[4] = w1.x; wkv[5] = w1.y; wkv[6] = w1.z; wkv[7] = w1.w;
+    }
+    const float denom = p.per_head ? (float)kD : (float)(p.heads * kD);
+    const int span = p.per_head ? 16 : 32;
+
+    long long i = 0;
+    bool failed = false;
+    for (;; i++) {
+        const long long row = (long long)blockIdx.x + i * gridDim.x;
+        if (row >= g.rows) break;  // CTA-uniform
+        const int s = (int)(i % g.stages);
+        const uint32_t ph = (uint32_t)((i / g.stages) & 1);
+        const bool ok = mbar_wait(bars + 8 * s, ph, ctl);
+        const unsigned char* st = ring_smem + (size_t)s * g.stage_bytes;
+        float xq[8], xk[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) xq[j] = xk[j] = 0.f;
+        float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+        uint4 vv = make_uint4(0u, 0u, 0u, 0u);
+        float sq = 0.f, sk = 0.f;
+        if (ok && act) {
+            if (p.q_out) {
+                unpack8(*reinterpret_cast<const uint4*>(st + 16 * t), xq);
+#pragma unroll
+                for (int j = 0; j < 8; j++) sq = __fadd_rn(sq, __fmul_rn(xq[j], xq[j]));
+            }
+            if (p.k_out) {
+                unpack8(*reinterpret_cast<const uint4*>(st + g.off_k + 16 * t), xk);
+#pragma unroll
+                for (int j = 0; j < 8; j++) sk = __fadd_rn(sk, __fmul_rn(xk[j], xk[j]));
+            }
+            if (p.v_out) vv = *reinterpret_cast<const uint4*>(st + g.off_v + 16 * t);
+            if (p.cosv) {
+                const float4* cp = reinterpret_cast<const float4*>(st + g.off_cos + 4 * pd);
+                const float4* sp = reinterpret_cast<const float4*>(st + g.off_sin + 4 * pd);
+                const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+                cs[0] = c0.x; cs[1] = c0.z; cs[2] = c1.x; cs[3] = c1.z;
+                sn[0] = s0.y; sn[1] = s0.w; sn[2] = s1.y; sn[3] = s1.w;
+            }
+        }
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            if (o < span) {
+                sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                sk += __shfl_xor_sync(0xffffffffu, sk, o);
+            }
+        }
+        float* rb = red + (i & 1) * 2 * nwarps;
+        if (lane == 0) {
+            rb[warp] = sq;
+            rb[nwarps + warp] = sk;
+        }
+        // One barrier per row: the reduction's, the verdict on the wait, and the release of stage s.
+        if (!__syncthreads_and(ok ? 1 : 0)) {
+            failed = true;
+            break;  // CTA-uniform
+        }
+        if (t == 0) {
+            const long long nrow = (long long)blockIdx.x + issued * gridDim.x;
+            if (nrow < g.rows) {
+                issue(nrow, s);
+                issued++;
+            }
+        }
+        if (!p.per_head) {
+            float a = 0.f, c = 0.f;
+            for (int w = 0; w < nwarps; w++) {
+                a += rb[w];
+                c += rb[nwarps + w];
+            }
+            sq = a;
+            sk = c;
+        }
+        if (!act) continue;
+        const int b = (int)(row / p.seq), srow = (int)(row % p.seq);
+        const size_t dst = (((size_t)b * p.heads + h) * p.seq + srow) * kD + pd;
+        if (p.v_out) *reinterpret_cast<uint4*>(p.v_out + dst) = vv;
+        auto finish = [&](const float (&x)[8], float ss, const float (&wv)[8], __nv_bfloat16* out) {
+            const float ms = __fdiv_rn(ss, denom);
+            const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, p.eps)));
+            float y[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) y[j] = __fmul_rn(__fmul_rn(x[j], inv), wv[j]);
+            float o[8];
+            if (p.cosv) {
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const float c = cs[j >> 1], sv = sn[j >> 1];
+                    o[j] = __fsub_rn(__fmul_rn(y[j], c), __fmul_rn(y[j + 1], sv));
+                    o[j + 1] = __fadd_rn(__fmul_rn(y[j], sv), __fmul_rn(y[j + 1], c));
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) o[j] = y[j];
+            }
+            *reinterpret_cast<uint4*>(out + dst) =
+                make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
+        };
+        if (p.q_out) finish(xq, sq, wqv, p.q_out);
+        if (p.k_out) finish(xk, sk, wkv, p.k_out);
+    }
+    // A wait ran out: copies already handed to the copy unit must land before the ring goes away.
+    if (failed && t == 0) {
+        for (long long j = i; j < issued; j++)
+            if (!mbar_drain(bars + 8 * (uint32_t)(j % g.stages), (uint32_t)((j / g.stages) & 1))) break;
+    }
+}
+
 }  // namespace fvprep
 
 extern "C" int fv_wan_qk_prep_bf16(void* stream, const void* proj, int width, int col_q, int col_k, int col_v,
@@ -193,6 +380,40 @@ extern "C" int fv_wan_qk_prep_bf16(void* stream, const void* proj, int width, in
     p.eps = eps;
     p.per_head = norm_scope == FV_NORM_PER_HEAD;
     const int threads = (heads * 16 + 31) & ~31;
+    const char* which = getenv("FV_PREP_KERNEL");  // "row": the one-CTA-per-row kernel (A/B timing)
+    if (!(which && which[0] == 'r')) {
+        // ring geometry: stage = q | k | v | cos | sin; as many stages as fit, several CTAs per SM for narrow rows
+        const uint32_t dimB = (uint32_t)dim * 2u;
+        fvprep::RingGeom g{};
+        g.off_k = dimB;
+        g.off_v = 2 * dimB;
+        g.off_cos = 3 * dimB;
+        g.off_sin = 3 * dimB + 512;
+        g.stage_bytes = 3 * dimB + 1024;
+        g.rows = (long long)batch * seq;
+        rc = fvrt::status_word(dev, &g.status);
+        if (rc != FV_RAN) return rc;
+        const int ctas_per_sm = threads <= 256 ? 4 : (threads <= 320 ? 2 : 1);
+        const uint32_t budget = (200u / (uint32_t)ctas_per_sm) * 1024u;
+        g.stages = (int)(budget / g.stage_bytes);
+        if (g.stages > 8) g.stages = 8;
+        if (g.stages < 2) g.stages = 2;
+        const size_t extra = 8 * (size_t)g.stages + 16 * (size_t)(threads / 32) + 16;
+        const size_t smem_ring = (size_t)g.stages * g.stage_bytes + extra;
+        int sms = 0;
+        FV_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        long long grid = (long long)sms * ctas_per_sm;
+        if (grid > g.rows) grid = g.rows;
+        auto run = [&](auto kern) -> int {
+            FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_ring));
+            kern<<<(unsigned)grid, threads, smem_ring, (cudaStream_t)stream>>>(p, g);
+            FV_CUDA(cudaGetLastError());
+            return FV_RAN;
+        };
+        if (threads <= 256) return run(fvprep::fv_wan_qk_prep_ring_kernel<256, 4>);
+        if (threads <= 640) return run(fvprep::fv_wan_qk_prep_ring_kernel<640, 1>);
+        return run(fvprep::fv_wan_qk_prep_ring_kernel<1024, 1>);
+    }
     const size_t smem = 2 * (threads / 32 + 1) * sizeof(float);
     // up to 40 heads: 640-thread blocks, two per SM (register cap 51); beyond: one block of up to 1024 threads
     if (threads <= 640)

@@ -39,6 +39,39 @@ def test_prep_matches_oracle(fvlib, oracle, batch, grid, heads, per_head):
         assert np.abs(got - want).max() <= np.abs(want).max() * 2.0 ** -8
 
 
+@pytest.mark.parametrize("batch,grid,heads,per_head", [(1, (3, 40, 50), 12, False), (2, (2, 30, 40), 40, False),
+                                                       (1, (3, 30, 40), 20, False), (1, (3, 20, 25), 48, False),
+                                                       (1, (3, 40, 50), 12, True), (1, (5, 40, 50), 1, False)])
+def test_prep_ring_turns_over_and_equals_the_row_kernel(fvlib, oracle, batch, grid, heads, per_head, monkeypatch):
+    """Enough rows that every persistent CTA refills its ring several times (each launch configuration of the
+    staged kernel: 4, 2 and 1 CTAs per SM, 640- and 1024-thread blocks): equal to the oracle on sampled rows,
+    and bit for bit to the one-CTA-per-row kernel everywhere."""
+    from fastvideo_rs_b200 import wan
+    seq = grid[0] * grid[1] * grid[2]
+    dim = heads * 128
+    proj = oracle.bf16_round(oracle.seeded_normal(33, heads, (batch, seq, 3 * dim)))
+    wq = (1.0 + 0.1 * oracle.seeded_normal(33, 1, (dim,))).astype(np.float32)
+    wk = (1.0 + 0.1 * oracle.seeded_normal(33, 2, (dim,))).astype(np.float32)
+    tc, ts = wan.wan_rope_tables(grid)
+    scope = wan.NORM_PER_HEAD if per_head else wan.NORM_ACROSS_HEADS
+    args = (to_dev_bf16(proj), torch.from_numpy(wq).cuda(), torch.from_numpy(wk).cuda(), tc, ts, heads)
+    monkeypatch.delenv("FV_PREP_KERNEL", raising=False)
+    q, k, v = wan.qk_prep(*args, norm_scope=scope)
+    from fastvideo_rs_b200 import sdpa
+    assert sdpa.device_status() == 0
+    monkeypatch.setenv("FV_PREP_KERNEL", "row")
+    q2, k2, v2 = wan.qk_prep(*args, norm_scope=scope)
+    monkeypatch.delenv("FV_PREP_KERNEL")
+    assert torch.equal(q, q2) and torch.equal(k, k2) and torch.equal(v, v2)
+    cos, sin = oracle.wan_rope(*grid)
+    want_q = oracle.qk_norm_rope_bhsd(proj, wq, cos, sin, batch, seq, heads, 128, 3 * dim, 0, 1e-6, per_head)
+    want_v = oracle.split_heads_bhsd(proj, batch, seq, heads, 128, 3 * dim, 2 * dim)
+    assert np.array_equal(to_host_f32(v).reshape(batch * heads, seq, 128), want_v)
+    gq = to_host_f32(q).reshape(batch * heads, seq, 128)
+    assert np.mean(gq != oracle.bf16_round(want_q)) < 2e-3
+    assert np.abs(gq - want_q).max() <= np.abs(want_q).max() * 2.0 ** -8
+
+
 def test_prep_without_rope_and_partial_outputs(fvlib, oracle):
     from fastvideo_rs_b200 import wan
     batch, seq, heads = 1, 50, 12
