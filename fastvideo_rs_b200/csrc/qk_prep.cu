@@ -9,7 +9,7 @@
 // host twin crates/fastvideo-cudarc/src/rt/ops.rs:2304-2350: inv = 1/sqrt(mean(x^2) + eps),
 // y = (x*inv)*w, even = y0*cos[s,even] - y1*sin[s,even+1], odd = y0*sin[s,even+1] + y1*cos[s,even],
 // every product and sum rounded separately (no fused multiply-add), then one rounding to bf16.
-// Only the order of the sum of squares differs (tree reduction instead of a sequential sum).
+// Only the sum of squares differs: fused multiply-adds in a tree instead of a sequential sum of rounded squares.
 #include "fv_ptx.cuh"
 #include "fv_runtime.h"
 #include <cuda_bf16.h>
@@ -48,6 +48,30 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
+}
+
+// Sum of the squares of 8 values on top of `acc` (fused multiply-adds: one rounding per term).
+__device__ __forceinline__ float sumsq8(const float (&x)[8], float acc) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc = fmaf(x[i], x[i], acc);
+    return acc;
+}
+// Butterfly over `span` lanes (16: the threads of one head, 32: the warp); every lane ends with the sum.
+__device__ __forceinline__ void lanes_sum(float& a, float& c, int span) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        if (o < span) {
+            a += __shfl_xor_sync(0xffffffffu, a, o);
+            c += __shfl_xor_sync(0xffffffffu, c, o);
+        }
+    }
+}
+// Row totals from the per-warp partial sums rb[0..nwarps) and rb[nwarps..2*nwarps): lane l takes warp l's
+// partials and the warp runs one more butterfly, so every thread gets the same bits in 2 loads.
+__device__ __forceinline__ void warps_sum(const float* rb, int nwarps, int lane, float& a, float& c) {
+    a = lane < nwarps ? rb[lane] : 0.f;
+    c = lane < nwarps ? rb[nwarps + lane] : 0.f;
+    lanes_sum(a, c, 32);
 }
 
 // One CTA per token row (b, s); thread t owns elements 8t..8t+7 of the heads*128 row, i.e.
@@ -93,23 +117,14 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_kernel(const Params
     float sq = 0.f, sk = 0.f;
     if (p.q_out && act) {
         unpack8(*reinterpret_cast<const uint4*>(src + p.col_q + 8 * t), xq);
-#pragma unroll
-        for (int i = 0; i < 8; i++) sq = __fadd_rn(sq, __fmul_rn(xq[i], xq[i]));
+        sq = sumsq8(xq, sq);
     }
     if (p.k_out && act) {
         unpack8(*reinterpret_cast<const uint4*>(src + p.col_k + 8 * t), xk);
-#pragma unroll
-        for (int i = 0; i < 8; i++) sk = __fadd_rn(sk, __fmul_rn(xk[i], xk[i]));
+        sk = sumsq8(xk, sk);
     }
     // Sum of squares: over the 16 threads of a head (per_head) or over the whole row.
-    const int span = p.per_head ? 16 : 32;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        if (o < span) {
-            sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            sk += __shfl_xor_sync(0xffffffffu, sk, o);
-        }
-    }
+    lanes_sum(sq, sk, p.per_head ? 16 : 32);
     float denom = (float)kD;
     if (!p.per_head) {
         if (lane == 0) {
@@ -117,13 +132,7 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_kernel(const Params
             red[nwarps + warp] = sk;
         }
         __syncthreads();
-        float a = 0.f, c = 0.f;
-        for (int w = 0; w < nwarps; w++) {
-            a += red[w];
-            c += red[nwarps + w];
-        }
-        sq = a;
-        sk = c;
+        warps_sum(red, nwarps, lane, sq, sk);
         denom = (float)(p.heads * kD);
     }
     if (!act) return;
@@ -197,7 +206,7 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_ring_kernel(const P
     if (p.k_out) row_bytes += dimB;
     if (p.v_out) row_bytes += dimB;
     if (p.cosv) row_bytes += 2u * kD * 4u;
-    auto issue = [&](long long row, int s) {  // one thread
+    auto issue = [&](long long row, int srow, int s) {  // one thread; srow = row % seq
         const uint32_t dst = base + (uint32_t)s * g.stage_bytes, bar = bars + 8 * s;
         const __nv_bfloat16* src = p.proj + (size_t)row * p.width;
         mbar_expect_tx(bar, row_bytes);
@@ -205,18 +214,30 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_ring_kernel(const P
         if (p.k_out) bulk_load(dst + g.off_k, src + p.col_k, dimB, bar);
         if (p.v_out) bulk_load(dst + g.off_v, src + p.col_v, dimB, bar);
         if (p.cosv) {
-            const size_t sidx = (size_t)(row % p.seq) * kD;
+            const size_t sidx = (size_t)srow * kD;
             bulk_load(dst + g.off_cos, p.cosv + sidx, kD * 4u, bar);
             bulk_load(dst + g.off_sin, p.sinv + sidx, kD * 4u, bar);
         }
     };
-    long long issued = 0;  // rows of this CTA handed to the copy unit (thread 0 only)
+    // Row indices advance by gridDim.x; (batch, position) follow by subtraction, the ring slot and its
+    // phase by counting: no division inside the loop.
+    const int step = (int)gridDim.x;
+    auto advance = [&](int& b, int& srow) {
+        srow += step;
+        while (srow >= p.seq) {
+            srow -= p.seq;
+            b++;
+        }
+    };
+    long long issued = 0;                    // rows of this CTA handed to the copy unit (thread 0 only)
+    long long nrow = (long long)blockIdx.x;  // next row to hand over, its batch and position, its slot
+    int nb = (int)(blockIdx.x / (unsigned)p.seq), nsrow = (int)(blockIdx.x % (unsigned)p.seq), nslot = 0;
     if (t == 0) {
-        for (int s = 0; s < g.stages; s++) {
-            const long long row = (long long)blockIdx.x + issued * gridDim.x;
-            if (row >= g.rows) break;
-            issue(row, s);
+        for (; nslot < g.stages && nrow < g.rows; nslot++) {
+            issue(nrow, nsrow, nslot);
             issued++;
+            nrow += step;
+            advance(nb, nsrow);
         }
     }
 
@@ -236,11 +257,10 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_ring_kernel(const P
 
     long long i = 0;
     bool failed = false;
-    for (;; i++) {
-        const long long row = (long long)blockIdx.x + i * gridDim.x;
-        if (row >= g.rows) break;  // CTA-uniform
-        const int s = (int)(i % g.stages);
-        const uint32_t ph = (uint32_t)((i / g.stages) & 1);
+    int b = (int)(blockIdx.x / (unsigned)p.seq), srow = (int)(blockIdx.x % (unsigned)p.seq);
+    int s = 0;
+    uint32_t ph = 0;
+    for (long long row = (long long)blockIdx.x; row < g.rows; row += step, i++) {  // CTA-uniform trip count
         const bool ok = mbar_wait(bars + 8 * s, ph, ctl);
         const unsigned char* st = ring_smem + (size_t)s * g.stage_bytes;
         float xq[8], xk[8];
@@ -252,13 +272,11 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_ring_kernel(const P
         if (ok && act) {
             if (p.q_out) {
                 unpack8(*reinterpret_cast<const uint4*>(st + 16 * t), xq);
-#pragma unroll
-                for (int j = 0; j < 8; j++) sq = __fadd_rn(sq, __fmul_rn(xq[j], xq[j]));
+                sq = sumsq8(xq, sq);
             }
             if (p.k_out) {
                 unpack8(*reinterpret_cast<const uint4*>(st + g.off_k + 16 * t), xk);
-#pragma unroll
-                for (int j = 0; j < 8; j++) sk = __fadd_rn(sk, __fmul_rn(xk[j], xk[j]));
+                sk = sumsq8(xk, sk);
             }
             if (p.v_out) vv = *reinterpret_cast<const uint4*>(st + g.off_v + 16 * t);
             if (p.cosv) {
@@ -269,13 +287,7 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_ring_kernel(const P
                 sn[0] = s0.y; sn[1] = s0.w; sn[2] = s1.y; sn[3] = s1.w;
             }
         }
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            if (o < span) {
-                sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                sk += __shfl_xor_sync(0xffffffffu, sk, o);
-            }
-        }
+        lanes_sum(sq, sk, span);
         float* rb = red + (i & 1) * 2 * nwarps;
         if (lane == 0) {
             rb[warp] = sq;
@@ -286,25 +298,20 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_ring_kernel(const P
             failed = true;
             break;  // CTA-uniform
         }
-        if (t == 0) {
-            const long long nrow = (long long)blockIdx.x + issued * gridDim.x;
-            if (nrow < g.rows) {
-                issue(nrow, s);
-                issued++;
-            }
+        if (t == 0 && nrow < g.rows) {  // the slot just read is the next one to fill
+            issue(nrow, nsrow, s);
+            issued++;
+            nrow += step;
+            advance(nb, nsrow);
         }
-        if (!p.per_head) {
-            float a = 0.f, c = 0.f;
-            for (int w = 0; w < nwarps; w++) {
-                a += rb[w];
-                c += rb[nwarps + w];
-            }
-            sq = a;
-            sk = c;
+        if (!p.per_head) warps_sum(rb, nwarps, lane, sq, sk);
+        const size_t dst = (((size_t)b * p.heads + h) * p.seq + srow) * kD + pd;
+        advance(b, srow);
+        if (++s == g.stages) {
+            s = 0;
+            ph ^= 1u;
         }
         if (!act) continue;
-        const int b = (int)(row / p.seq), srow = (int)(row % p.seq);
-        const size_t dst = (((size_t)b * p.heads + h) * p.seq + srow) * kD + pd;
         if (p.v_out) *reinterpret_cast<uint4*>(p.v_out + dst) = vv;
         auto finish = [&](const float (&x)[8], float ss, const float (&wv)[8], __nv_bfloat16* out) {
             const float ms = __fdiv_rn(ss, denom);
