@@ -94,6 +94,32 @@ class SpLayout:
     def needs_padding(self) -> bool:
         return self.len != self.seg_rows
 
+    def needed_ranks(self, causal: Optional[BlockCausal]) -> List[int]:
+        """The other ranks whose shard holds a key some row of this shard may see.  Dense: all of them.  Under
+        the block-causal mask (rt/attn.rs:448-453) the rows [start, start + len) see the keys
+        [lo, hi) and [0, sink * block): hi = the end of the last row's block (it may reach into the next shard),
+        lo = the start of the oldest block inside the first row's window (0 without a window)."""
+        others = [r for r in range(self.world) if r != self.rank]
+        if causal is None or self.len == 0:
+            return others if self.len else []
+        bt = max(causal.block_tokens, 1)
+        first, last = self.start, self.start + self.len - 1
+        hi = min(self.seq, (last // bt + 1) * bt)
+        lo = max(0, first // bt - causal.window + 1) * bt if causal.window > 0 else 0
+        sink_hi = min(self.seq, causal.sink * bt)
+        need = []
+        for r in others:
+            s0, l = self.ranges[r]
+            if l > 0 and ((s0 < hi and s0 + l > lo) or s0 < sink_hi):
+                need.append(r)
+        return need
+
+    def pass2_for(self, causal: Optional[BlockCausal]):
+        """pass2() with the segments of ranks no row can see emptied: their shards are not fetched."""
+        need = set(self.needed_ranks(causal))
+        lens = [l if r in need else 0 for r, (_, l) in enumerate(self.ranges)]
+        return lens, [s for s, _ in self.ranges]
+
 
 class SpAttention:
     """Sequence-parallel dense attention for one (seq, bh) shape; buffers allocated once.
@@ -159,12 +185,15 @@ class SpAttention:
                     self.exchange, self.stage, self.hdl = "nccl", None, None
 
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """q, k, v: this rank's [bh, len_r, 128] bf16 shards.  Returns this rank's [bh, len_r, 128] bf16."""
+                out: Optional[torch.Tensor] = None, causal: Optional[BlockCausal] = None) -> torch.Tensor:
+        """q, k, v: this rank's [bh, len_r, 128] bf16 shards.  Returns this rank's [bh, len_r, 128] bf16.
+        causal: the block-causal mask over GLOBAL token indices; a rank then fetches only the shards its rows
+        can see (later ranks do more work than earlier ones: contiguous shards are kept, as the reference's)."""
         d = q.shape[-1]
         scale = float(scale) if scale is not None else 1.0 / d ** 0.5
         if self.world == 1:
-            return segments_fwd(q, k, v, [self.len], [0], self.len, scale, out=out)
+            return segments_fwd(q, k, v, [self.len], [0], self.len, scale, out=out, causal=causal)
+        need = self.layout.needed_ranks(causal)
         cur = torch.cuda.current_stream(self.device)
         if out is None:
             out = torch.empty((self.bh, self.len, d), dtype=torch.bfloat16, device=q.device)
@@ -190,7 +219,7 @@ class SpAttention:
                 for g in range(G):
                     for step in range(1, self.world):
                         r = (self.rank - step) % self.world
-                        if not no_comm:
+                        if not no_comm and r in need:
                             with torch.cuda.stream(self.copy_streams[(step - 1) % len(self.copy_streams)]):
                                 self.k_all[g][r].copy_(self.peer[r][0, g * n:(g + 1) * n], non_blocking=True)
                                 self.v_all[g][r].copy_(self.peer[r][1, g * n:(g + 1) * n], non_blocking=True)
@@ -225,12 +254,16 @@ class SpAttention:
                     arrived.append(ev)
         # pass 1: the local keys, every head, while the exchange is in flight
         l1, s1 = self.layout.pass1()
-        segments_fwd(q, ks, vs, l1, s1, self.seg_rows, scale, out=self.o1, lse_out=self.lse1)
+        l2, s2 = self.layout.pass2_for(causal)
+        if not any(l2):  # no row of this shard sees a key of another shard: pass 1 is the result
+            segments_fwd(q, ks, vs, l1, s1, self.seg_rows, scale, out=out, causal=causal, q_row0=self.start)
+            return out
+        segments_fwd(q, ks, vs, l1, s1, self.seg_rows, scale, out=self.o1, lse_out=self.lse1, causal=causal,
+                     q_row0=self.start)
         # pass 2 per head group, as it arrives: every other rank's keys, merged with pass 1
-        l2, s2 = self.layout.pass2()
         for g in range(G):
             cur.wait_event(arrived[g])
             sl = slice(g * n, (g + 1) * n)
             segments_fwd(q[sl], self.k_all[g], self.v_all[g], l2, s2, self.seg_rows, scale, out=out[sl],
-                         prev_o=self.o1[sl], prev_lse=self.lse1[sl])
+                         prev_o=self.o1[sl], prev_lse=self.lse1[sl], causal=causal, q_row0=self.start)
         return out

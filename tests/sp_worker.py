@@ -15,6 +15,7 @@ sys.path.insert(0, str(ROOT))
 def main():
     seq = int(sys.argv[1]) if len(sys.argv) > 1 else 3001
     bh = int(sys.argv[2]) if len(sys.argv) > 2 else 3
+    block = int(sys.argv[3]) if len(sys.argv) > 3 else 0  # > 0: block-causal mask with that many tokens per block
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -24,13 +25,14 @@ def main():
     dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to("cuda", torch.bfloat16)
     attn = sp.SpAttention(seq, bh)
     s0, n = attn.start, attn.len
+    causal = sdpa.BlockCausal(block, 0, 0) if block else None
     out = None
     for _ in range(2):  # twice: the gather buffers are reused
-        out = attn.forward(dev(q[:, s0:s0 + n]), dev(k[:, s0:s0 + n]), dev(v[:, s0:s0 + n]))
+        out = attn.forward(dev(q[:, s0:s0 + n]), dev(k[:, s0:s0 + n]), dev(v[:, s0:s0 + n]), causal=causal)
     torch.cuda.synchronize()
     assert sdpa.device_status() == 0
     rows = np.unique(np.concatenate([np.arange(s0, s0 + min(n, 40)), np.arange(s0 + max(n - 40, 0), s0 + n)])).astype(np.int32)
-    want = O.sdpa_rows(q, k, v, rows=rows)
+    want = O.sdpa_rows(q, k, v, rows=rows, block_causal=(block, 0, 0) if block else None)
     got = out.float().cpu().numpy()[:, rows - s0]
     err = np.abs(got - want)
     ok = bool(err.max() <= 2e-2 and err.mean() <= 2e-3 and np.isfinite(got).all())

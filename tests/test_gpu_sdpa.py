@@ -186,6 +186,53 @@ def test_two_pass_segments_equal_one_pass(fvlib, oracle):
     assert np.abs(to_host_f32(lse) - want_lse).max() < 2e-2
 
 
+@pytest.mark.parametrize("world,bt,win,sink", [(2, 100, 0, 0), (3, 130, 0, 0), (4, 64, 2, 1), (3, 1000, 0, 0), (4, 37, 3, 0)])
+def test_sequence_parallel_block_causal_rank_by_rank(fvlib, oracle, world, bt, win, sink):
+    """What each rank of SpAttention.forward(causal=...) launches, run rank after rank on one GPU: pass 1 over the
+    rank's own keys, pass 2 over the shards SpLayout says it needs, both under the mask with global row and key
+    indices.  The shards put together equal the one-launch masked kernel and the masked oracle."""
+    from fastvideo_rs_b200 import sdpa, sp
+    bh, seq = 2, 1001  # uneven shards: the gathered buffer is padded
+    q, k, v = qkv(oracle, 77 + world, bh, seq, seq)
+    tq, tk, tv = to_dev_bf16(q), to_dev_bf16(k), to_dev_bf16(v)
+    causal = sdpa.BlockCausal(bt, win, sink)
+    scale = 1.0 / math.sqrt(128)
+    layouts = [sp.SpLayout(seq, world, r) for r in range(world)]
+    rows = layouts[0].seg_rows
+    k_all = torch.zeros((world, bh, rows, 128), dtype=torch.bfloat16, device="cuda")
+    v_all = torch.zeros_like(k_all)
+    for r, lay in enumerate(layouts):
+        k_all[r, :, : lay.len] = tk[:, lay.start : lay.start + lay.len]
+        v_all[r, :, : lay.len] = tv[:, lay.start : lay.start + lay.len]
+    parts = []
+    for r, lay in enumerate(layouts):
+        qr = tq[:, lay.start : lay.start + lay.len].contiguous()
+        l1, s1 = lay.pass1()
+        l2, s2 = lay.pass2_for(causal)
+        # a rank holds nothing of the shards it does not need: poison them
+        ka, va = k_all.clone(), v_all.clone()
+        for o in range(world):
+            if o != r and o not in lay.needed_ranks(causal):
+                ka[o].fill_(float("nan"))
+                va[o].fill_(float("nan"))
+        if not any(l2):
+            parts.append(sp.segments_fwd(qr, k_all[r].contiguous(), v_all[r].contiguous(), l1, s1, rows, scale, causal=causal,
+                                         q_row0=lay.start))
+            continue
+        o1 = torch.empty((bh, lay.len, 128), dtype=torch.float32, device="cuda")
+        lse1 = torch.empty((bh, lay.len), dtype=torch.float32, device="cuda")
+        sp.segments_fwd(qr, k_all[r].contiguous(), v_all[r].contiguous(), l1, s1, rows, scale, out=o1, lse_out=lse1,
+                        causal=causal, q_row0=lay.start)
+        parts.append(sp.segments_fwd(qr, ka, va, l2, s2, rows, scale, prev_o=o1, prev_lse=lse1, causal=causal,
+                                     q_row0=lay.start))
+    assert sdpa.device_status() == 0
+    got = torch.cat(parts, dim=1)
+    assert torch.isfinite(got.float()).all()
+    one = sdpa.dense_fwd(tq, tk, tv, causal=causal)
+    assert float((got.float() - one.float()).abs().max()) <= 2e-2
+    assert_close(to_host_f32(got), oracle.sdpa_rows(q, k, v, block_causal=(bt, win, sink)), f"sp{world} causal bt{bt} w{win} s{sink}")
+
+
 def test_merged_heads_output_is_the_permuted_bhsd_output(fvlib, oracle):
     """merge_heads folded into the store (rt/ops.rs:2373-2385): same bits as the BHSD call, [b, s, h*d] order."""
     from fastvideo_rs_b200 import sdpa

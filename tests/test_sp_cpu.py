@@ -116,3 +116,30 @@ def test_layout_tables(fvlib):
     assert torch.equal(sp.all_gather_seq(parts, 2), x)
     with pytest.raises(ValueError):
         sp.all_gather_seq([], 2)
+
+
+def test_needed_ranks_under_the_block_causal_mask():
+    """Which shards a rank fetches: checked against the predicate itself on every (row, key) pair."""
+    from fastvideo_rs_b200 import sp
+    from fastvideo_rs_b200.sdpa import BlockCausal
+    for seq, world in ((1001, 4), (960, 8), (37, 3), (5, 8)):
+        for bc in (BlockCausal(100), BlockCausal(64, 2, 1), BlockCausal(37, 3, 0), BlockCausal(1000), BlockCausal(1, 1, 0),
+                   BlockCausal(7, 0, 2)):
+            for rank in range(world):
+                lay = sp.SpLayout(seq, world, rank)
+                need = set(lay.needed_ranks(bc))
+                truth = set()
+                for o, (s0, l) in enumerate(lay.ranges):
+                    if o == rank:
+                        continue
+                    if any(bc.allows(qi, ki) for qi in range(lay.start, lay.start + lay.len) for ki in range(s0, s0 + l)):
+                        truth.add(o)
+                # never misses a shard a row can see; may keep one whose keys fall between two rows' windows
+                assert truth <= need, (seq, world, bc, rank, truth, need)
+                if bc.window == 0:
+                    assert truth == need, (seq, world, bc, rank, truth, need)
+                lens, starts = lay.pass2_for(bc)
+                assert [i for i, l in enumerate(lens) if l] == sorted(need)
+                assert starts == [s for s, _ in lay.ranges]
+        lay = sp.SpLayout(seq, world, 0)
+        assert lay.needed_ranks(None) == [r for r in range(1, world)] or lay.len == 0
