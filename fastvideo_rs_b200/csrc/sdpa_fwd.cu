@@ -308,7 +308,7 @@ static int splitkv_choose(long long bh, long long sq, long long sk, int sms) {
     for (int s = 2; s <= kMaxSplits; s++) {
         if (sk % s != 0 || sk / s < 4 * kBN || bh * s > 0x7fffffffll) continue;
         const double us = splitkv_cost(bh, sq, sk, s, sms);
-        if (us < 0.97 * best_us) {  // a split has to pay for itself by more than the model's noise
+        if (us < 0.93 * best_us) {  // a split has to pay for itself by more than the model's error (a few per cent)
             best = s;
             best_us = us;
         }
