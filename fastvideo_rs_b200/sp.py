@@ -267,3 +267,53 @@ class SpAttention:
             segments_fwd(q[sl], self.k_all[g], self.v_all[g], l2, s2, self.seg_rows, scale, out=out[sl],
                          prev_o=self.o1[sl], prev_lse=self.lse1[sl], causal=causal, q_row0=self.start)
         return out
+
+
+class NativeSp:
+    """The same sequence-parallel attention with the whole sequence of launches behind the C ABI
+    (fv_sp_create / fv_sp_forward_bf16: NCCL all-gather on the handle's own high-priority stream, two passes),
+    for hosts that are not Python.  `unique_id`: the 128 bytes of `NativeSp.unique_id()` made on rank 0 and handed
+    to every rank (here: by torch.distributed, in a Rust host: by whatever it has).  One handle per rank."""
+
+    def __init__(self, seq: int, bh: int, world: int, rank: int, unique_id: Optional[bytes] = None, groups: int = 0):
+        self.seq, self.bh, self.world, self.rank = seq, bh, world, rank
+        self._h = ctypes.c_void_p()
+        buf = ctypes.create_string_buffer(unique_id, 128) if unique_id is not None else None
+        rc = _lib.lib().fv_sp_create(buf, world, rank, seq, bh, groups, ctypes.byref(self._h))
+        _lib.check(rc, "fv_sp_create")
+        st, ln, rows, gr = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        _lib.check(_lib.lib().fv_sp_info(self._h, ctypes.byref(st), ctypes.byref(ln), ctypes.byref(rows), ctypes.byref(gr)),
+                   "fv_sp_info")
+        self.start, self.len, self.seg_rows, self.groups = st.value, ln.value, rows.value, gr.value
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = ctypes.create_string_buffer(128)
+        _lib.check(_lib.lib().fv_sp_unique_id(buf), "fv_sp_unique_id")
+        return buf.raw
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None,
+                out: Optional[torch.Tensor] = None, out_bf16: bool = True,
+                causal: Optional[BlockCausal] = None) -> torch.Tensor:
+        """q, k, v: this rank's [bh, len, 128] bf16 shards -> this rank's [bh, len, 128]."""
+        scale = float(scale) if scale is not None else 1.0 / q.shape[-1] ** 0.5
+        if out is None:
+            out = torch.empty((self.bh, self.len, 128), dtype=torch.bfloat16 if out_bf16 else torch.float32, device=q.device)
+        mode, bt, win, sink = (1, causal.block_tokens, causal.window, causal.sink) if causal else (0, 0, 0, 0)
+        vp = lambda t: ctypes.c_void_p(t.data_ptr())
+        with torch.cuda.device(q.device):
+            rc = _lib.lib().fv_sp_forward_bf16(self._h, _stream_ptr(), vp(q), vp(k), vp(v), vp(out),
+                                               int(out.dtype == torch.bfloat16), ctypes.c_float(scale), mode, bt, win, sink)
+        _lib.check(rc, "fv_sp_forward_bf16")
+        return out
+
+    def close(self) -> None:
+        if self._h:
+            _lib.lib().fv_sp_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

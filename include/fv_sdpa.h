@@ -335,6 +335,38 @@ FV_API int fv_sdpa_ws(void* stream, const void* q, const void* k, const void* v,
  * remainder going to the low ranks.  start and len are host arrays of `world` ints. */
 FV_API void fv_shard_ranges(int seq, int world, int* start, int* len);
 
+/* ---- sequence-parallel attention, one handle per rank ---------------------------------------
+ * Replaces dispatch_sharded_multi_gpu (crates/fastvideo-cudarc/src/rt/sdpa.rs:354-410: K/V replicated on
+ * every rank, outputs gathered through the host) by: contiguous token shards of q, k, v on every rank
+ * (fv_shard_ranges), ONE exchange per call -- an NCCL all-gather of the bf16 K and V shards into this rank's
+ * own HBM on a high-priority stream of the handle -- overlapped with attention over the local keys, then a
+ * second pass over the other ranks' keys that merges the first by log-sum-exp.  The output stays sharded.
+ * One rank per GPU (a process or a thread with that GPU current).  NCCL is looked up at run time
+ * (libnccl.so.2); without it the calls that need it return FV_ERR_NCCL.
+ *
+ * fv_sp_unique_id: 128 bytes (an ncclUniqueId) that rank 0 makes and hands to every rank by the host's own
+ *   means.  Host pointer.
+ * fv_sp_create: collective over the `world` ranks (ncclCommInitRank), world <= FV_MAX_SEGMENTS; allocates the
+ *   handle's buffers on the current device (gathered K/V: 2 * world * bh * seg_rows * 256 bytes; the first
+ *   pass' f32 result; a zero-padded copy of the shard when shards are uneven).  groups <= 0: the heads are
+ *   exchanged in 2 groups from 8 ranks on, else 1 (the second pass of a group starts when that group has
+ *   arrived).  world == 1 needs neither an id nor NCCL.  unique_id: host pointer.
+ * fv_sp_info: this rank's first token, its shard length, the longest shard, the head groups.
+ * fv_sp_forward_bf16: q, k, v [bh, len, 128] bf16 shards of this rank, out [bh, len, 128] bf16 or f32.
+ *   mask_mode FV_MASK_BLOCK_CAUSAL applies the mask of fv_sdpa_dense_bf16 over GLOBAL token indices; shards no
+ *   row of this rank can see are left out of the second pass.  Asynchronous on `stream` (on return `stream`
+ *   is ordered after the exchange, so k and v may be rewritten by later work on it); calls on one handle must
+ *   be issued in the same order on every rank and from one stream at a time.  A rank without rows (more ranks
+ *   than tokens) still calls: it takes part in the exchange and computes nothing (its operands may be null).
+ * fv_sp_destroy: frees the handle (synchronise the streams that used it first).
+ */
+FV_API int fv_sp_unique_id(void* id_out_128_bytes);
+FV_API int fv_sp_create(const void* unique_id, int world, int rank, int seq, int bh, int groups, void** sp_out);
+FV_API int fv_sp_info(void* sp, int* start, int* len, int* seg_rows, int* groups);
+FV_API int fv_sp_forward_bf16(void* sp, void* stream, const void* q, const void* k, const void* v, void* out,
+                              int out_is_bf16, float scale, int mask_mode, int block_tokens, int window, int sink);
+FV_API int fv_sp_destroy(void* sp);
+
 #ifdef __cplusplus
 }
 #endif

@@ -16,6 +16,7 @@ def main():
     seq = int(sys.argv[1]) if len(sys.argv) > 1 else 3001
     bh = int(sys.argv[2]) if len(sys.argv) > 2 else 3
     block = int(sys.argv[3]) if len(sys.argv) > 3 else 0  # > 0: block-causal mask with that many tokens per block
+    native = len(sys.argv) > 4 and sys.argv[4] == "native"  # the C-ABI handle (fv_sp_*) instead of the Python class
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -23,7 +24,12 @@ def main():
     from oracle import oracle as O
     q, k, v = (O.bf16_round(O.seeded_normal(61, i, (bh, seq, 128))) for i in range(3))
     dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to("cuda", torch.bfloat16)
-    attn = sp.SpAttention(seq, bh)
+    if native:
+        ids = [sp.NativeSp.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        attn = sp.NativeSp(seq, bh, world, rank, ids[0])
+    else:
+        attn = sp.SpAttention(seq, bh)
     s0, n = attn.start, attn.len
     causal = sdpa.BlockCausal(block, 0, 0) if block else None
     out = None

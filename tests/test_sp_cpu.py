@@ -143,3 +143,29 @@ def test_needed_ranks_under_the_block_causal_mask():
                 assert starts == [s for s, _ in lay.ranges]
         lay = sp.SpLayout(seq, world, 0)
         assert lay.needed_ranks(None) == [r for r in range(1, world)] or lay.len == 0
+
+
+def test_native_sp_handle_argument_checks_without_a_gpu():
+    """fv_sp_create validates before it touches a device; with no sm_100 device it says so instead of
+    computing anywhere else."""
+    import ctypes
+    import torch
+    from fastvideo_rs_b200 import _lib
+    L = _lib.lib()
+    h = ctypes.c_void_p()
+    for world, rank, seq, bh in ((2, 2, 100, 4), (0, 0, 100, 4), (9, 0, 100, 4), (1, 0, 0, 4), (1, 0, 100, 0), (2, -1, 100, 4)):
+        assert L.fv_sp_create(None, world, rank, seq, bh, 0, ctypes.byref(h)) == _lib.ERR_INVALID, (world, rank, seq, bh)
+        assert not h.value
+    assert L.fv_sp_create(None, 2, 0, 100, 4, 0, ctypes.byref(h)) == _lib.ERR_INVALID  # two ranks need an id
+    assert "communicator id" in _lib.last_error()
+    assert L.fv_sp_info(None, None, None, None, None) == _lib.ERR_INVALID
+    assert L.fv_sp_forward_bf16(None, None, None, None, None, None, 1, ctypes.c_float(0.1), 0, 0, 0, 0) == _lib.ERR_INVALID
+    assert L.fv_sp_destroy(None) == _lib.RAN
+    if not torch.cuda.is_available():
+        assert L.fv_sp_create(None, 1, 0, 100, 4, 0, ctypes.byref(h)) == _lib.ERR_NO_DEVICE
+        assert not h.value
+    # the id comes from NCCL itself when it can be loaded; either way the call answers, it does not crash
+    buf = ctypes.create_string_buffer(128)
+    rc = L.fv_sp_unique_id(buf)
+    assert rc in (_lib.RAN, _lib.ERR_NCCL), _lib.last_error()
+    assert L.fv_sp_unique_id(None) == _lib.ERR_INVALID
