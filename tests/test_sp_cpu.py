@@ -169,3 +169,14 @@ def test_native_sp_handle_argument_checks_without_a_gpu():
     rc = L.fv_sp_unique_id(buf)
     assert rc in (_lib.RAN, _lib.ERR_NCCL), _lib.last_error()
     assert L.fv_sp_unique_id(None) == _lib.ERR_INVALID
+
+
+def test_dense_second_pass_table_is_unchanged_by_the_mask_plumbing():
+    """Without a mask the shard selection keeps every other rank: pass2_for(None) is pass2()."""
+    from fastvideo_rs_b200 import sp
+    for seq, world in ((75600, 8), (75600, 4), (32760, 2), (1001, 3), (5, 8)):
+        for rank in range(world):
+            lay = sp.SpLayout(seq, world, rank)
+            if lay.len:
+                assert lay.pass2_for(None) == lay.pass2()
+                assert lay.needed_ranks(None) == [r for r in range(world) if r != rank]
