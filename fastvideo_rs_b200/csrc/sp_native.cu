@@ -99,13 +99,14 @@ static void release(Sp* s) {
 
 // The other ranks whose shard holds a key some row of this shard may see (all of them without a mask); the
 // block-causal predicate is crates/fastvideo-cudarc/src/rt/attn.rs:448-453.
-static void visible_lens(const Sp* s, int mask_mode, int bt, int window, int sink, int* lens_out) {
-    for (int r = 0; r < s->world; r++) lens_out[r] = r == s->rank ? 0 : s->lens[r];
-    if (mask_mode != FV_MASK_BLOCK_CAUSAL || s->len == 0) return;
+static void visible_lens(int seq, int world, int rank, const int* starts, const int* lens, int mask_mode, int bt,
+                         int window, int sink, int* lens_out) {
+    for (int r = 0; r < world; r++) lens_out[r] = r == rank ? 0 : lens[r];
+    if (mask_mode != FV_MASK_BLOCK_CAUSAL || lens[rank] == 0) return;
     if (bt < 1) bt = 1;
-    const long long first = s->start, last = (long long)s->start + s->len - 1;
+    const long long first = starts[rank], last = (long long)starts[rank] + lens[rank] - 1;
     long long hi = (last / bt + 1) * bt;
-    if (hi > s->seq) hi = s->seq;
+    if (hi > seq) hi = seq;
     long long lo = 0;
     if (window > 0) {
         lo = first / bt - window + 1;
@@ -113,10 +114,10 @@ static void visible_lens(const Sp* s, int mask_mode, int bt, int window, int sin
         lo *= bt;
     }
     long long sink_hi = (long long)sink * bt;
-    if (sink_hi > s->seq) sink_hi = s->seq;
-    for (int r = 0; r < s->world; r++) {
-        if (r == s->rank) continue;
-        const long long s0 = s->starts[r], l = s->lens[r];
+    if (sink_hi > seq) sink_hi = seq;
+    for (int r = 0; r < world; r++) {
+        if (r == rank) continue;
+        const long long s0 = starts[r], l = lens[r];
         const bool vis = l > 0 && ((s0 < hi && s0 + l > lo) || s0 < sink_hi);
         if (!vis) lens_out[r] = 0;
     }
@@ -161,7 +162,7 @@ static int forward(Sp* s, cudaStream_t stream, const void* q, const void* k, con
         return FV_RAN;
     }
     std::vector<int> lens2(s->world);
-    visible_lens(s, mask_mode, bt, window, sink, lens2.data());
+    visible_lens(s->seq, s->world, s->rank, s->starts.data(), s->lens.data(), mask_mode, bt, window, sink, lens2.data());
     bool any = false;
     for (int r = 0; r < s->world; r++) any = any || lens2[r] > 0;
     const int len1 = s->len, start1 = s->start;
@@ -275,6 +276,17 @@ extern "C" int fv_sp_unique_id(void* id_out) {
     fvsp::NcclId id;
     FV_NCCL(fvsp::g_nccl.GetUniqueId(&id));
     memcpy(id_out, id.bytes, sizeof(id.bytes));
+    return FV_RAN;
+}
+
+extern "C" int fv_sp_second_pass_lens(int seq, int world, int rank, int mask_mode, int block_tokens, int window, int sink,
+                                      int* lens_out) {
+    fvrt::clear_error();
+    if (world < 1 || world > FV_MAX_SEGMENTS || rank < 0 || rank >= world || seq < 1 || !lens_out)
+        return fvrt::fail(FV_ERR_INVALID, "sp: rank %d of %d ranks, %d tokens", rank, world, seq);
+    int starts[FV_MAX_SEGMENTS], lens[FV_MAX_SEGMENTS];
+    fv_shard_ranges(seq, world, starts, lens);
+    fvsp::visible_lens(seq, world, rank, starts, lens, mask_mode, block_tokens, window, sink, lens_out);
     return FV_RAN;
 }
 

@@ -360,6 +360,11 @@ FV_API void fv_shard_ranges(int seq, int world, int* start, int* len);
  *   than tokens) still calls: it takes part in the exchange and computes nothing (its operands may be null).
  * fv_sp_destroy: frees the handle (synchronise the streams that used it first).
  */
+/* The segment lengths fv_sp_forward_bf16 gives its second pass on `rank` (host arithmetic only, no device needed):
+ * lens_out[r] (host, `world` ints) = the shard length of rank r if some row of `rank` can see one of its keys under
+ * the mask, else 0; 0 for `rank` itself. */
+FV_API int fv_sp_second_pass_lens(int seq, int world, int rank, int mask_mode, int block_tokens, int window, int sink,
+                                  int* lens_out);
 FV_API int fv_sp_unique_id(void* id_out_128_bytes);
 FV_API int fv_sp_create(const void* unique_id, int world, int rank, int seq, int bh, int groups, void** sp_out);
 FV_API int fv_sp_info(void* sp, int* start, int* len, int* seg_rows, int* groups);

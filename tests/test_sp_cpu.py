@@ -180,3 +180,27 @@ def test_dense_second_pass_table_is_unchanged_by_the_mask_plumbing():
             if lay.len:
                 assert lay.pass2_for(None) == lay.pass2()
                 assert lay.needed_ranks(None) == [r for r in range(world) if r != rank]
+
+
+def test_native_second_pass_table_equals_the_python_layout():
+    """The shard selection inside fv_sp_forward_bf16 (C++) against SpLayout.pass2_for (Python), masks and none."""
+    import ctypes
+    from fastvideo_rs_b200 import _lib, sp
+    from fastvideo_rs_b200.sdpa import BlockCausal
+    L = _lib.lib()
+    masks = [None, BlockCausal(100), BlockCausal(64, 2, 1), BlockCausal(37, 3, 0), BlockCausal(1000), BlockCausal(1, 1, 0),
+             BlockCausal(7, 0, 2), BlockCausal(4680), BlockCausal(390, 4, 1)]
+    for seq, world in ((1001, 4), (960, 8), (37, 3), (5, 8), (32760, 8), (75600, 2), (1, 1)):
+        for bc in masks:
+            for rank in range(world):
+                lens = (ctypes.c_int * world)()
+                mode, bt, win, sink = (1, bc.block_tokens, bc.window, bc.sink) if bc else (0, 0, 0, 0)
+                assert L.fv_sp_second_pass_lens(seq, world, rank, mode, bt, win, sink, lens) == _lib.RAN
+                lay = sp.SpLayout(seq, world, rank)
+                want = lay.pass2_for(bc)[0] if lay.len else [0 if r == rank else l for r, (_, l) in enumerate(lay.ranges)]
+                if lay.len == 0 and bc is not None:
+                    continue  # a rank without rows computes nothing: its table is not used
+                assert list(lens) == want, (seq, world, rank, bc, list(lens), want)
+    lens = (ctypes.c_int * 8)()
+    assert L.fv_sp_second_pass_lens(100, 9, 0, 0, 0, 0, 0, lens) == _lib.ERR_INVALID
+    assert L.fv_sp_second_pass_lens(100, 2, 2, 0, 0, 0, 0, lens) == _lib.ERR_INVALID
