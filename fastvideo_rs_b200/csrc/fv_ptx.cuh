@@ -54,6 +54,7 @@ struct WaitCtl {
     volatile int* abort_smem;
     int* status;
     int role;
+    long long limit = FV_WAIT_CYCLES;  // cycles a wait may last before the role gives up
 };
 
 // Bounded wait on phase `parity`.  Returns false after a timeout or when
@@ -65,7 +66,7 @@ FV_DEV bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtl& c) {
     while (!mbar_try(bar, parity)) {
         if (((++n) & 63u) == 0u) {
             if (*c.abort_smem) return false;
-            if (clock64() - t0 > FV_WAIT_CYCLES) {
+            if (clock64() - t0 > c.limit) {
                 *c.abort_smem = 1;
                 atomicCAS(c.status, FV_ST_OK, FV_ST_TIMEOUT_BASE + c.role);
                 return false;
@@ -173,6 +174,12 @@ FV_DEV void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[128]) {
 FV_DEV void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 " FV_L32_A ", [%32];" : FV_O32(r, 0) : "r"(taddr) : "memory");
 }
+// The same for register arrays of other sizes: 32 columns into r[OFF .. OFF+31].
+template <int OFF, int N>
+FV_DEV void tmem_ld32_at(uint32_t taddr, uint32_t (&r)[N]) {
+    static_assert(OFF + 32 <= N, "tmem_ld32_at: out of range");
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 " FV_L32_A ", [%32];" : FV_O32(r, OFF) : "r"(taddr) : "memory");
+}
 FV_DEV void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 FV_DEV void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // Orders every later use of r after the preceding volatile asm (the wait):
@@ -186,6 +193,16 @@ FV_DEV void tmem_pin(uint32_t (&r)[N]) {
 // Store 32 registers to 32 consecutive TMEM columns of this thread's lane.
 FV_DEV void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], " FV_L32_B ";" ::"r"(taddr), FV_I32(r, 0) : "memory");
+}
+
+// Store 16 registers r[OFF .. OFF+15] to 16 consecutive TMEM columns of this thread's lane.
+template <int OFF, int N>
+FV_DEV void tmem_st16_at(uint32_t taddr, const uint32_t (&r)[N]) {
+    static_assert(OFF + 16 <= N, "tmem_st16_at: out of range");
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), FV_I16(r, OFF)
+        : "memory");
 }
 
 // --------------------------------------------------------------------- math

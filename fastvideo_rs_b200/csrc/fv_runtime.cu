@@ -2,6 +2,7 @@
 #include <mutex>
 #include <stdio.h>
 #include <string.h>
+#include <stdlib.h>
 
 namespace fvrt {
 
@@ -19,7 +20,11 @@ void clear_error() { g_err[0] = 0; }
 static const int kMaxDev = 64;
 static std::mutex g_mu;
 static int g_sm[kMaxDev];      // 0 = not probed, else major*10+minor
+static int g_sms[kMaxDev];     // 0 = not probed, else the number of SMs
 static int* g_status[kMaxDev];
+// The kernels' status word (and room to spare): part of the module image, zero at load, one instance
+// per device that loads the library.  Host code only ever uses its address, taken once per device.
+static __device__ __align__(256) int fv_status_block[64];
 
 int require_sm100(int* device_out) {
     int dev = -1;
@@ -52,12 +57,44 @@ int status_word(int device, int** ptr_out) {
     std::lock_guard<std::mutex> lk(g_mu);
     if (!g_status[device]) {
         int* p = nullptr;
-        FV_CUDA(cudaMalloc(&p, 256));
-        FV_CUDA(cudaMemset(p, 0, 256));
+        cudaError_t e = cudaGetSymbolAddress((void**)&p, fv_status_block);  // `device` is current (require_sm100)
+        if (e != cudaSuccess || !p)
+            return fail(FV_ERR_CUDA, "cudaGetSymbolAddress(status block) on device %d: %s", device, cudaGetErrorString(e));
         g_status[device] = p;
     }
     *ptr_out = g_status[device];
     return FV_RAN;
+}
+
+int sm_count(int device, int* out) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_sms[device]) {
+        int n = 0;
+        FV_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device));
+        g_sms[device] = n > 0 ? n : 1;
+    }
+    *out = g_sms[device];
+    return FV_RAN;
+}
+
+static thread_local char g_last_kernel[256] = "";
+static bool g_logged[kLogKeys];
+
+void ran(LogKey key, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_last_kernel, sizeof(g_last_kernel), fmt, ap);
+    va_end(ap);
+    bool first;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        first = !g_logged[key];
+        g_logged[key] = true;
+    }
+    if (first) {
+        const char* e = getenv("FV_LOG");
+        if (!e || strcmp(e, "0") != 0) fprintf(stderr, "fvsdpa: %s\n", g_last_kernel);
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -90,8 +127,44 @@ int encode_map4(CUtensorMap* map, const void* base, const uint64_t dims[4], cons
     return FV_RAN;
 }
 
+struct MapKey {
+    const void* base;
+    uint64_t dims[4], strides[3];
+    uint32_t box_rows;
+};
+static const int kMapSlots = 32;
+static MapKey g_map_key[kMapSlots];
+static CUtensorMap g_map_val[kMapSlots];
+static int g_map_used = 0, g_map_next = 0;
+
+int encode_map4_cached(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint64_t strides[3],
+                       uint32_t box_rows) {
+    MapKey k;
+    memset(&k, 0, sizeof(k));
+    k.base = base;
+    for (int i = 0; i < 4; i++) k.dims[i] = dims[i];
+    for (int i = 0; i < 3; i++) k.strides[i] = strides[i];
+    k.box_rows = box_rows;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        for (int i = 0; i < g_map_used; i++)
+            if (memcmp(&g_map_key[i], &k, sizeof(k)) == 0) {
+                *map = g_map_val[i];
+                return FV_RAN;
+            }
+    }
+    const int rc = encode_map4(map, base, dims, strides, box_rows);
+    if (rc != FV_RAN) return rc;
+    std::lock_guard<std::mutex> lk(g_mu);
+    const int slot = g_map_used < kMapSlots ? g_map_used++ : (g_map_next++ % kMapSlots);
+    g_map_key[slot] = k;
+    g_map_val[slot] = *map;
+    return FV_RAN;
+}
+
 }  // namespace fvrt
 
+extern "C" const char* fv_last_kernel(void) { return fvrt::g_last_kernel; }
 extern "C" const char* fv_last_error(void) { return fvrt::g_err; }
 extern "C" const char* fv_version(void) { return "fvsdpa 0.1 (sm_100a)"; }
 

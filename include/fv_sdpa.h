@@ -44,7 +44,7 @@ extern "C" {
 #define FV_NORM_ACROSS_HEADS 0
 #define FV_NORM_PER_HEAD 1
 
-#define FV_MAX_SEGMENTS 8
+#define FV_MAX_SEGMENTS 16
 
 /* Text of the calling thread's last error ("" if none).  Host pointer, valid until the next call. */
 FV_API const char* fv_last_error(void);
@@ -54,8 +54,24 @@ FV_API const char* fv_version(void);
 
 /* Reads and clears the current device's kernel status word.  Synchronises `stream`.
  * Returns FV_RAN when every kernel finished its waits, FV_ERR_DEVICE_STATUS when one
- * gave up (code in *code_out: 100 + role), FV_ERR_CUDA on a CUDA error. */
+ * gave up (code in *code_out: 100 + role), FV_ERR_CUDA on a CUDA error.
+ * The word is part of the library's module image (a file-scope __device__ array, zero at load): every
+ * kernel of the library reports there, the two-pass call on built-in scratch included, and neither this
+ * call nor any launch allocates for it. */
 FV_API int fv_device_status(void* stream, int* code_out);
+
+/* One line naming the kernel the calling thread's last successful call launched, with its launch shape
+ * ("" before the first).  The first launch of each kind of kernel in a process also prints that line on
+ * stderr (FV_LOG=0 silences it) -- the counterpart of the reference's log-once lines
+ * (crates/fastvideo-cudarc/src/rt/attn.rs:306-310, rt/ops.rs:1385-1401). */
+FV_API const char* fv_last_kernel(void);
+
+/* Failure-path self-test: launches ONE CTA of one warp that waits, with a budget of `cycles` clock cycles
+ * (1e3 .. 2e9), on a barrier nobody arrives at.  The wait runs out, the kernel records status 109 and
+ * returns normally; the next fv_device_status then answers FV_ERR_DEVICE_STATUS.  Nothing traps and the
+ * context stays usable: this is how a host checks its handling of a kernel that gave up.  No counterpart
+ * in the reference (its debug build traps instead, crates/fastvideo-cudarc/src/rt/attn_dc.cu:89-105). */
+FV_API int fv_selftest_wait_timeout(void* stream, long long cycles);
 
 /* ---- dense / block-causal SDPA -------------------------------------------------
  * Replaces rt::attn_dc::dense_fwd (crates/fastvideo-cudarc/src/rt/attn_dc.rs:213-273)
@@ -119,26 +135,38 @@ FV_API int fv_sdpa_segments_bf16(void* stream, const void* q, const void* k, con
                           float scale, int mask_mode, int block_tokens, int window, int sink, int q_row0,
                           float* lse_out, const float* prev_o, const float* prev_lse);
 
+/* fv_sdpa_segments_bf16 for a query shard made of TWO runs of the sequence: rows [0, q_split) have global
+ * indices q_row0 + i, rows [q_split, sq) have q_row1 + (i - q_split) (q_split = 0: one run).  This is the
+ * shard a rank holds under a zig-zag split of a causally masked sequence (an early and a late piece, so
+ * that every rank sees about the same number of keys).  The reference shards contiguously only
+ * (crates/fastvideo-cudarc/src/rt/sp.rs:16-28) and does not shard its block-causal route at all
+ * (rt/sdpa_rule.rs:523-532). */
+FV_API int fv_sdpa_segments_runs_bf16(void* stream, const void* q, const void* k, const void* v, void* out,
+                                      int out_is_bf16, int bh, int sq, int nseg, const int* seg_len,
+                                      const int* seg_start, int seg_rows, float scale, int mask_mode,
+                                      int block_tokens, int window, int sink, int q_row0, int q_split, int q_row1,
+                                      float* lse_out, const float* prev_o, const float* prev_lse);
+
 /* Two-pass attention without any allocation -- no counterpart in the reference.
  *
  * For hosts that may not allocate device memory where they call attention: a serving loop with a fixed
  * memory budget, a real-time thread that must not take the allocator's device-wide synchronisation, a
  * runtime whose buffers all come from a pool sized at start-up.  The other entry points need scratch from
- * somewhere (the library's status word comes from cudaMalloc on a device's first call; the pass-1 result of
- * a two-pass evaluation is a caller buffer).  This one computes the same thing as fv_sdpa_segments_bf16
+ * somewhere (the pass-1 result of a two-pass evaluation is a caller buffer; the split-KV parts are a caller
+ * workspace).  This one computes the same thing as fv_sdpa_segments_bf16
  * called twice -- pass 1 over the local keys (k_local / v_local: one segment of local_len keys starting at
  * global index local_start, local_rows rows per head in memory), pass 2 over the gathered segments
  * (k_all / v_all as in fv_sdpa_segments_bf16; give the local segment length 0 there) merging pass 1 -- and
- * keeps the status word and the pass-1 result (f32 [bh, sq, 128] + [bh, sq]) in a fixed array inside the
- * library.  It calls no cudaMalloc, cudaFree or other allocating routine.
+ * keeps the pass-1 result (f32 [bh, sq, 128] + [bh, sq]) in a fixed array inside the library.  A bounded wait
+ * that runs out inside it is reported through fv_device_status like any other.  It calls no cudaMalloc, cudaFree or other allocating routine.
  *   Limit: bh * sq <= 65 024 rows (the array is about 32 MiB per GPU, held until the process exits);
  *     larger calls return FV_ERR_INVALID with the numbers in fv_last_error().
  *   remote_ready_event: optional cudaEvent_t; pass 2 waits for it on `stream` (record it after the K/V
  *     all-gather on the communication stream), so pass 1 overlaps the exchange.
  *   The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
  *     device current); make that first call before any stream capture.
- *   Every call uses the same array: the status word is cleared at the start of each call, the pass-1 area
- *     is overwritten.  Calls that overlap on one GPU (two streams, two threads) race on it -- serialise them.
+ *   Every call uses the same array: nothing in it has to start at zero (pass 1 writes every row that pass 2
+ *     reads), the pass-1 area is simply overwritten.  Calls that overlap on one GPU (two streams, two threads) race on it -- serialise them.
  *   Dense only (no mask). */
 FV_API int fv_sdpa_two_pass_noalloc_bf16(void* stream, const void* q, const void* k_local, const void* v_local,
                                          int local_len, int local_start, int local_rows, const void* k_all,

@@ -3,7 +3,10 @@
 // same bf16 inputs, and times each case with CUDA events.  No torch, no
 // Python: it exists so that a kernel change can be checked in seconds.
 //
-//   sdpa_check [--bench] [--case bh,sq,sk[,block_tokens,window,sink]]...
+//   sdpa_check [--bench] [--selftest] [--case bh,sq,sk[,block_tokens,window,sink]]...
+//
+// --selftest also drives the bounded-wait failure path (fv_selftest_wait_timeout) and checks that
+// fv_device_status reports it once and that a normal case runs afterwards.
 //
 // Exit code 0 when every case is within tolerance (max-abs 2e-2, mean-abs
 // 2e-3 against the f64 evaluation) and no kernel reported a status.
@@ -225,11 +228,34 @@ static int run_case(const Case& c, bool bench, int out_bf16) {
     return pass ? 0 : 1;
 }
 
+static int selftest() {
+    int rc = fv_selftest_wait_timeout(nullptr, 2000000);
+    if (rc != FV_RAN) {
+        printf("selftest: launch rc=%d %s\n", rc, fv_last_error());
+        return 1;
+    }
+    CK(cudaDeviceSynchronize());
+    int code = 0;
+    rc = fv_device_status(nullptr, &code);
+    if (rc != FV_ERR_DEVICE_STATUS || code != 109) {
+        printf("selftest: expected FV_ERR_DEVICE_STATUS / 109, got rc=%d code=%d\n", rc, code);
+        return 1;
+    }
+    rc = fv_device_status(nullptr, &code);
+    if (rc != FV_RAN || code != 0) {
+        printf("selftest: the status word was not cleared (rc=%d code=%d)\n", rc, code);
+        return 1;
+    }
+    printf("{\"case\": \"selftest: a wait ran out, status 109 reported once\", \"pass\": true}\n");
+    return run_case(Case{2, 300, 512, 0, 0, 0}, false, 1);
+}
+
 int main(int argc, char** argv) {
-    bool bench = false;
+    bool bench = false, st = false;
     std::vector<Case> cases;
     for (int i = 1; i < argc; i++) {
         if (!strcmp(argv[i], "--bench")) bench = true;
+        else if (!strcmp(argv[i], "--selftest")) st = true;
         else if (!strcmp(argv[i], "--case") && i + 1 < argc) {
             Case c{1, 1, 1, 0, 0, 0};
             sscanf(argv[++i], "%d,%d,%d,%d,%d,%d", &c.bh, &c.sq, &c.sk, &c.bt, &c.win, &c.sink);
@@ -241,7 +267,11 @@ int main(int argc, char** argv) {
                             {2, 63, 4097, 0, 0, 0}, {2, 130, 1, 0, 0, 0},    {2, 300, 512, 0, 0, 0},  {2, 1000, 333, 0, 0, 0},
                             {4, 1024, 1024, 0, 0, 0}, {2, 257, 640, 0, 0, 0}, {2, 2048, 2048, 0, 0, 0},
                             {2, 600, 600, 100, 0, 0}, {2, 600, 600, 100, 2, 1}, {2, 1000, 1000, 130, 0, 0},
-                            {1, 24, 24, 5, 2, 1},   {2, 2340, 2340, 780, 0, 0}};
+                            {1, 24, 24, 5, 2, 1},   {2, 2340, 2340, 780, 0, 0},
+                            // more work items than SMs: every CTA takes several, Q ring and barrier phases wrap
+                            {160, 512, 384, 0, 0, 0}, {8, 8192, 1024, 0, 0, 0}, {40, 2000, 640, 0, 0, 0},
+                            {12, 4680, 4680, 1560, 0, 0}, {24, 3000, 512, 0, 0, 0}, {300, 130, 257, 0, 0, 0},
+                            {20, 2500, 2500, 600, 2, 1}};
         for (const Case& c : def) cases.push_back(c);
     }
     int bad = 0;
@@ -250,6 +280,7 @@ int main(int argc, char** argv) {
     }
     // f32 output on one small case
     if (argc == 1) bad += run_case(Case{2, 300, 512, 0, 0, 0}, false, 0);
+    if (st) bad += selftest();
     printf("%s (%d failing)\n", bad ? "FAIL" : "OK", bad);
     return bad ? 1 : 0;
 }
