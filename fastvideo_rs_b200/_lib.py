@@ -56,6 +56,8 @@ def lib() -> ctypes.CDLL:
         _lib = ctypes.CDLL(str(LIB_PATH))
         _lib.fv_last_error.restype = ctypes.c_char_p
         _lib.fv_version.restype = ctypes.c_char_p
+        _lib.fv_last_kernel.restype = ctypes.c_char_p
+        _lib.fv_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_longlong]
         for name in ("fv_probe_live", "fv_probe_default", "fv_shard_ranges", "fv_rule_shape_of"):
             getattr(_lib, name).restype = None
     return _lib
@@ -72,3 +74,8 @@ def check(rc: int, what: str) -> None:
 
 def last_error() -> str:
     return lib().fv_last_error().decode()
+
+
+def last_kernel() -> str:
+    """One line naming the kernel this thread's last successful call launched."""
+    return lib().fv_last_kernel().decode()

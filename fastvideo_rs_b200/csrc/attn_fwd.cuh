@@ -9,36 +9,59 @@
 // * One CTA per SM for the whole launch.  Work items (256 query rows of one plane = two 128-row
 //   accumulator tiles, "A" and "B") are dealt round-robin: CTA c takes items c, c + grid, ...
 //   Under a causal mask the items of a plane are ordered heaviest first.
-// * 20 warps.  The launch gives every thread 96 registers; the four softmax warpgroups then take 104
-//   each and the fifth warpgroup (loader, issuer, two idle warps) drops to 64: 512 x 104 + 128 x 64
-//   is exactly the 640 x 96 the CTA owns.
-//     warps 0-15   softmax.  Warp w serves row tile w / 8, score columns 64 * ((w / 4) % 2) .. + 63,
-//                  TMEM lanes 32 * (w % 4) .. + 31: TWO threads share a query row, each holding half
-//                  of its 128 scores.  The two warps of a row sit on the same scheduler, so the MUFU
-//                  and FMA latencies of one half hide under the other; the time from "S complete" to
-//                  "P complete", which bounds the tensor pipe in a two-tile ping-pong, is about half
-//                  of what one thread per row needs.
-//     warp 16      loader: one thread issues every TMA copy (Q ring of 3 x 32 KB, K/V ring of
+// * 12 warps = three warpgroups.  The launch gives every thread 168 registers; the two softmax
+//   warpgroups then take 216 each and the third drops to 72 (256 x 216 + 128 x 72 = 384 x 168):
+//     warps 0-7    softmax: warp w serves row tile w / 4, TMEM lanes 32 (w % 4) .. + 31 (thread =
+//                  TMEM lane = query row, the only mapping the 32x32b TMEM load offers).
+//     warp 8       loader: one thread issues every TMA copy (Q ring of 3 x 32 KB, K/V ring of
 //                  4 x 32 KB) and runs one item ahead with the Q tiles.
-//     warp 17      issuer: one thread issues every tcgen05.mma; the warp owns the TMEM allocation.
-// * TMEM (512 columns): row tile t owns columns 256 t .. 256 t + 255: scores S at +0 (128 f32
-//   columns), output accumulator O at +128.  The bf16 probabilities of half h overwrite the first
-//   32 of that half's own 64 score columns (+64 h .. +64 h + 31), so neither thread of a row ever
-//   touches a column the other one still has to read.
-// * Per key tile j the issuer runs, for t = A then B:  O_t += P_t(j-1) . V(j-1);  S_t = Q_t . K(j)^T.
-//   P is handed over in two steps (the first 32 keys of each half, then the rest), so the first four
-//   K=16 slices of P.V start while the second half of the exponentials is still being evaluated.
-// * Softmax in the base-2 domain with a LAZY reference: the per-row reference m only moves when a
-//   tile's maximum exceeds it by more than 2^8, in which case O (TMEM) and the row sum are rescaled.
-//   The two threads of a row agree on the tile maximum through 2 bytes of shared memory each (the
-//   maximum rounded UP to bf16: any common reference at or above the true maximum is exact) and one
-//   64-thread mbarrier phase; the row sums are added once per item.
-// * Every wait is bounded (fv_ptx.cuh): a role that gives up records a code in the status word,
-//   raises the CTA's abort flag, and every role falls through to the common exit, where copies in
-//   flight are awaited, the issuer's last MMA is awaited and TMEM is freed.  No trap, no endless spin.
+//     warp 9       issuer: one thread issues every tcgen05.mma; the warp owns the TMEM allocation.
+//     warps 10-11  idle (they make the third warpgroup whole).
+// * TMEM (512 columns): scores S_A, S_B (128 f32 columns each), then the output accumulators O_A,
+//   O_B.  The bf16 probabilities P overwrite S from its column 0 on (64 columns), always behind the
+//   columns still to be read.  (With S and O of a tile side by side instead, the P.V products, which
+//   read P and update O at once, ran measurably slower.)
+// * Per key tile j the issuer runs, for t = A then B:  O_t += P_t(j-1) . V(j-1);  S_t = Q_t . K(j)^T,
+//   so one row tile's softmax runs under the other's MMAs.  That only works while a softmax step is
+//   shorter than the other tile's two MMAs (1024 tensor-pipe cycles); a longer one makes both tiles'
+//   softmax warps run at the same time on the same schedulers, which doubles it again.  Hence:
+// * P is handed to the issuer in two steps (keys 0-63, then 64-127), so the first half of P.V runs while
+//   the second half of the exponentials is still being evaluated.
+// * STREAMING softmax without a maximum pass.  Base-2 domain, lazy reference m per row: P = 2^(s -
+//   m) is evaluated straight away against the reference the row already has, 32 columns at a time as
+//   they come out of TMEM (loads double-buffered), and each half row's sum of P is the proof that this
+//   was safe: every P is positive, so sum(P) <= 2^40 implies max(P) <= 2^40, far inside what bf16 P and
+//   f32 accumulators hold, and a reference that lags the true maximum by any amount cancels exactly
+//   when O is divided by the row sum.  Only when a sum exceeds the guard (or the row has no reference
+//   yet: the first tile of an item) does the warp take the exact path: read S again (what it needs is
+//   still there), take the row maxima, move the references, rescale O and the row sums, evaluate P
+//   again; if it is the second half that trips, the first half is already with the issuer, and the warp
+//   waits for that product to finish before it touches O.  On N(0,1) inputs the exact path runs on the
+//   first tile of each item and nowhere else.
+// * Every wait is bounded: a role that gives up records a code in the status word, raises the CTA's
+//   abort flag, and every role falls through to the common exit, where copies in flight are awaited,
+//   the issuer's last MMA is awaited and TMEM is freed.  No trap, no endless spin.
 #pragma once
 #include <cuda.h>
 #include "fv_ptx.cuh"
+
+// Build-time tuning (every setting computes the same function):
+//   FV_ATT_POLY     every FV_ATT_POLY-th pair of an unmasked tile's exponentials is evaluated on the FMA pipe
+//                   instead of MUFU (0 = none, 4 = a quarter, 8 = an eighth, 2 = a half).  Both tiles' softmax
+//                   warps share one MUFU pipe per scheduler (4 results per cycle), which at 128 x 128
+//                   exponentials per tile is exactly as long as the tile's two MMAs: moving a share of them
+//                   to the FMA pipe, evenly interleaved, is what lets the two overlap.
+//   FV_ATT_SPLIT    TMEM map: 1 = S_A S_B O_A O_B, 0 = S_A O_A S_B O_B (no measurable difference)
+//   FV_ATT_BACKOFF  nanoseconds a waiting thread sleeps between two probes of its barrier (0 = none)
+#ifndef FV_ATT_POLY
+#define FV_ATT_POLY 0
+#endif
+#ifndef FV_ATT_SPLIT
+#define FV_ATT_SPLIT 1
+#endif
+#ifndef FV_ATT_BACKOFF
+#define FV_ATT_BACKOFF 0
+#endif
 
 #define FV_ST_BAD_SMEM 90  // dynamic shared memory is not 1024-byte aligned (the swizzled tiles need it)
 
@@ -48,34 +71,33 @@ constexpr int kD = 128;
 constexpr int kKeyTile = 128;   // keys per score tile: N of Q.K^T, K extent of P.V
 constexpr int kRowTile = 128;   // query rows per accumulator: M of both products
 constexpr int kItemRows = 256;  // one work item = row tiles A and B
-constexpr int kWarps = 20;          // registers are allotted per four warps: 18 would be charged as 20
+constexpr int kWarps = 12;
 constexpr int kThreads = kWarps * 32;
-constexpr int kSoftmaxWarps = 16;
-constexpr int kLoaderWarp = 16;
-constexpr int kIssuerWarp = 17;
+constexpr int kSoftmaxWarps = 8;
+constexpr int kLoaderWarp = 8;
+constexpr int kIssuerWarp = 9;
 constexpr int kQSlots = 3;
 constexpr int kKvSlots = 4;
 constexpr uint32_t kSlotBytes = 32768;   // 128 rows x 128 bf16: two 64-column swizzled panels
 constexpr uint32_t kPanelBytes = 16384;
 constexpr int kMaxSeg = 16;
-constexpr float kSlackLog2 = 8.0f;
+constexpr float kGuard = 1099511627776.f;  // 2^40: a row sum of P above this sends the tile down the exact path
 constexpr uint32_t kFullWarp = 0xffffffffu;
 
 // Shared-memory map, offsets from the (1024-byte aligned) start of dynamic shared memory.
 struct Smem {
     static constexpr uint32_t q = 0;
     static constexpr uint32_t kv = q + kQSlots * kSlotBytes;
-    static constexpr uint32_t xch = kv + kKvSlots * kSlotBytes;  // u16 [row tile 2][parity 2][half 2][row 128]
-    static constexpr uint32_t q_full = xch + 2048;               // mbarriers, 8 bytes each
+    static constexpr uint32_t q_full = kv + kKvSlots * kSlotBytes;  // mbarriers, 8 bytes each
     static constexpr uint32_t q_free = q_full + 8 * kQSlots;
     static constexpr uint32_t kv_full = q_free + 8 * kQSlots;
     static constexpr uint32_t kv_free = kv_full + 8 * kKvSlots;
     static constexpr uint32_t s_ready = kv_free + 8 * kKvSlots;  // [2] S_t complete (issuer -> softmax)
-    static constexpr uint32_t p_early = s_ready + 16;            // [2] first 32 keys of each half of P_t stored
+    static constexpr uint32_t p_early = s_ready + 16;            // [2] keys 0-63 of P_t stored (softmax -> issuer)
     static constexpr uint32_t p_ready = p_early + 16;            // [2] all of P_t stored
-    static constexpr uint32_t o_ready = p_ready + 16;            // [2] O_t of the item complete
-    static constexpr uint32_t pair = o_ready + 16;               // [8] the two warps of a (row tile, lane quarter)
-    static constexpr uint32_t drain = pair + 64;
+    static constexpr uint32_t pv_early = p_ready + 16;           // [2] the product over keys 0-63 has run (issuer -> softmax)
+    static constexpr uint32_t o_ready = pv_early + 16;           // [2] O_t of the item complete
+    static constexpr uint32_t drain = o_ready + 16;
     static constexpr uint32_t tmem_slot = drain + 8;
     static constexpr uint32_t abort_flag = tmem_slot + 4;
     static constexpr uint32_t total = abort_flag + 4;
@@ -107,6 +129,11 @@ struct Job {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL) || !defined(__CUDA_ARCH__)
 
 using namespace fvp;
+
+// TMEM columns of row tile t: its scores (the probabilities overwrite them from the first column on)
+// and its output accumulator.
+FV_DEV uint32_t tmem_scores(uint32_t t) { return FV_ATT_SPLIT ? 128u * t : 256u * t; }
+FV_DEV uint32_t tmem_output(uint32_t t) { return FV_ATT_SPLIT ? 256u + 128u * t : 256u * t + 128u; }
 
 FV_DEV float neg_inf() { return __int_as_float(0xff800000); }
 FV_DEV float as_f(uint32_t u) { return __uint_as_float(u); }
@@ -145,14 +172,39 @@ FV_DEV int global_row(const Job& jb, int r) {
 struct Item {
     int plane, q0;
 };
+// Work item number i.  Dense launches: plane-major, so the CTAs running at any one time share a few
+// planes' K and V in L2.  Masked launches (jb.heavy_first): by falling cost, i.e. query block from the
+// last to the first, every plane's copy of a block side by side.
 FV_DEV Item item_at(const Job& jb, int i) {
     Item it;
-    it.plane = i / jb.q_blocks;
-    int qb = i - it.plane * jb.q_blocks;
-    if (jb.heavy_first) qb = jb.q_blocks - 1 - qb;
-    it.q0 = qb * kItemRows;
+    if (jb.heavy_first) {
+        const int qb = jb.q_blocks - 1 - i / jb.planes;
+        it.plane = i - (i / jb.planes) * jb.planes;
+        it.q0 = qb * kItemRows;
+    } else {
+        it.plane = i / jb.q_blocks;
+        it.q0 = (i - it.plane * jb.q_blocks) * kItemRows;
+    }
     return it;
 }
+// The items of this CTA, in order: round r deals items r * grid .. r * grid + grid - 1, left to right
+// in even rounds and right to left in odd ones.  With the items sorted by falling cost, a CTA that got
+// the heaviest of one round gets the lightest of the next, and all CTAs end at about the same time.
+struct Deal {
+    int round = 0;
+    FV_DEV int next(const Job& jb) {
+        const int g = (int)gridDim.x, c = (int)blockIdx.x;
+        const int i = round * g + (((round & 1) && jb.heavy_first) ? g - 1 - c : c);
+        round++;
+        return i < jb.items ? i : -1;
+    }
+    // (in an odd round of a masked launch the last, partial round is dealt from the right: the CTAs on the left,
+    // which carried the heavier items of the round before, stay idle)
+    FV_DEV int peek(const Job& jb) const {
+        Deal d = *this;
+        return d.next(jb);
+    }
+};
 
 // The key tiles an item visits, in the order every role walks them.
 struct KeyTile {
@@ -192,92 +244,63 @@ FV_DEV int count_tiles(const Job& jb, const Span& sp) {
 }
 
 // ------------------------------------------------------------------------------------------ MMA
+// The issuing thread is the pace-maker of the whole CTA: a tcgen05.mma of this size occupies the tensor
+// pipe for 64 cycles, and one thread executing dependent integer instructions at one per four to six
+// cycles falls behind as soon as an MMA costs it more than about ten instructions.  So every group of
+// MMAs is ONE asm statement whose descriptors are the group's base descriptor plus a constant (in the
+// 16-byte address field), two adds per MMA, and the thread keeps next to nothing in registers.
+#define FV_MMA_SS "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+#define FV_MMA_TS "tcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
+#define FV_QK_STEP(off) "add.s64 a, %1, " #off ";\n\tadd.s64 b, %2, " #off ";\n\t" FV_MMA_SS
+#define FV_PV_STEP(col, off) "add.u32 t, %1, " #col ";\n\tadd.s64 b, %2, " #off ";\n\t" FV_MMA_TS
+
 // S (128 x 128 f32, TMEM) = Q (128 rows, K-major, 128-byte swizzle) . K^T (128 keys, same layout):
-// eight K=16 slices along the head dim.  Slice s sits 32 bytes further inside a 64-column panel,
-// slices 4-7 in the second panel; the descriptor's address field counts 16-byte units.
-FV_DEV void scores_mma(uint32_t tS, uint32_t q_smem, uint32_t k_smem) {
+// eight K=16 slices along the head dim.  Slice s sits 32 bytes (2 address units) further inside a
+// 64-column panel, slices 4-7 in the second panel 16 KB (1024 units) on.
+FV_DEV void scores_mma(uint32_t tS, uint64_t qd, uint64_t kd) {
     constexpr uint32_t idesc = umma_idesc_bf16(kRowTile, kKeyTile, 0);
-    const uint64_t qd = umma_desc_sw128(q_smem, 16, 1024), kd = umma_desc_sw128(k_smem, 16, 1024);
-#pragma unroll
-    for (int s = 0; s < 8; s++) {
-        const uint64_t step = (uint64_t)((s & 3) * 2 + (s >> 2) * (int)(kPanelBytes >> 4));
-        umma_ss(tS, qd + step, kd + step, idesc, s > 0 ? 1u : 0u);
-    }
+    asm volatile(
+        "{\n\t.reg .pred pt, pf;\n\t.reg .b64 a, b;\n\t"
+        "setp.ne.b32 pf, %3, %3;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+        FV_QK_STEP(2) FV_QK_STEP(4) FV_QK_STEP(6) FV_QK_STEP(1024) FV_QK_STEP(1026) FV_QK_STEP(1028) FV_QK_STEP(1030)
+        "}"
+        ::"r"(tS), "l"(qd), "l"(kd), "r"(idesc)
+        : "memory");
 }
-// O (128 x 128 f32, TMEM) (+)= P . V over the K=16 key slices named in SLICES (bit s = keys 16 s .. 16 s + 15).
-// P comes from TMEM: slice s at column 64 (s / 4) + 8 (s % 4) of the row tile's score block.  V is
-// MN-major in shared memory: 64-column panels 16 KB apart, 8-key groups 1024 bytes apart.
-template <uint32_t SLICES>
-FV_DEV void output_mma(uint32_t tO, uint32_t tS, uint32_t v_smem, bool fresh) {
+// O (128 x 128 f32, TMEM) (+)= P . V.  P comes from TMEM: key slice s (16 keys) at column 8 s of the
+// row tile's score block.  V is MN-major in shared memory (64-column
+// panels 16 KB apart, 8-key groups 1024 bytes apart): slice s starts 2 KB = 128 address units further.
+// Two statements of four slices: keys 0-63 (the first slice overwrites O when `fresh`) and keys 64-127.
+FV_DEV void output_mma_early(uint32_t tO, uint32_t tP, uint64_t vd, bool fresh) {
     constexpr uint32_t idesc = umma_idesc_bf16(kRowTile, kD, 1);
-    const uint64_t vd = umma_desc_sw128(v_smem, kPanelBytes, 1024);
-    uint32_t acc = fresh ? 0u : 1u;
-#pragma unroll
-    for (int s = 0; s < 8; s++) {
-        if (((SLICES >> s) & 1u) == 0u) continue;
-        umma_ts(tO, tS + 64u * (uint32_t)(s >> 2) + 8u * (uint32_t)(s & 3), vd + (uint64_t)(s * 128), idesc, acc);
-        acc = 1u;
-    }
+    asm volatile(
+        "{\n\t.reg .pred pt, p0;\n\t.reg .b64 b;\n\t.reg .b32 t;\n\t"
+        "setp.eq.b32 p0, %4, 0;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+        FV_PV_STEP(8, 128) FV_PV_STEP(16, 256) FV_PV_STEP(24, 384)
+        "}"
+        ::"r"(tO), "r"(tP), "l"(vd), "r"(idesc), "r"(fresh ? 1u : 0u)
+        : "memory");
+}
+FV_DEV void output_mma_late(uint32_t tO, uint32_t tP, uint64_t vd) {
+    constexpr uint32_t idesc = umma_idesc_bf16(kRowTile, kD, 1);
+    asm volatile(
+        "{\n\t.reg .pred pt;\n\t.reg .b64 b;\n\t.reg .b32 t;\n\t"
+        "setp.eq.b32 pt, %3, %3;\n\t"
+        FV_PV_STEP(32, 512) FV_PV_STEP(40, 640) FV_PV_STEP(48, 768) FV_PV_STEP(56, 896)
+        "}"
+        ::"r"(tO), "r"(tP), "l"(vd), "r"(idesc)
+        : "memory");
 }
 
 // -------------------------------------------------------------------------------------- softmax
-// 2^(u * sl2 + noff) for columns C0 .. C0 + 31 of this thread's half row: packed bf16 pairs into
-// pw[C0 / 2 .. C0 / 2 + 15], returns the f32 sum.  POLY: every fourth pair on the FMA pipe
-// (fvp::ex2_poly_x2) instead of MUFU; only for tiles without masked columns, because the
-// polynomial never returns an exact zero.
-template <int C0, bool POLY>
-FV_DEV float exp_chunk(const uint32_t (&u)[64], uint32_t (&pw)[32], float sl2, float noff) {
-    uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
-    const uint64_t s2 = pack_f32x2(sl2, sl2), nf = pack_f32x2(noff, noff);
-#pragma unroll
-    for (int w = 0; w < 16; w++) {
-        const int c = C0 + 2 * w;
-        float t0, t1, p0, p1;
-        unpack_f32x2(fma_f32x2(pack_f32x2(as_f(u[c]), as_f(u[c + 1])), s2, nf), t0, t1);
-        if (POLY && (w & 3) == 3) {
-            ex2_poly_x2(t0, t1, p0, p1);
-        } else {
-            p0 = ex2(t0);
-            p1 = ex2(t1);
-        }
-        const uint64_t pp = pack_f32x2(p0, p1);
-        if (w & 1) acc1 = add_f32x2(acc1, pp);
-        else acc0 = add_f32x2(acc0, pp);
-        pw[C0 / 2 + w] = pack_bf16x2(p0, p1);
-    }
-    float a, b, c, d;
-    unpack_f32x2(acc0, a, b);
-    unpack_f32x2(acc1, c, d);
-    return (a + b) + (c + d);
-}
-
-FV_DEV float max64(const uint32_t (&u)[64]) {
-    float x0 = max3(as_f(u[0]), as_f(u[1]), as_f(u[2])), x1 = max3(as_f(u[3]), as_f(u[4]), as_f(u[5]));
-    float x2 = max3(as_f(u[6]), as_f(u[7]), as_f(u[8])), x3 = max3(as_f(u[9]), as_f(u[10]), as_f(u[11]));
-#pragma unroll
-    for (int c = 12; c < 60; c += 8) {
-        x0 = max3(x0, as_f(u[c]), as_f(u[c + 1]));
-        x1 = max3(x1, as_f(u[c + 2]), as_f(u[c + 3]));
-        x2 = max3(x2, as_f(u[c + 4]), as_f(u[c + 5]));
-        x3 = max3(x3, as_f(u[c + 6]), as_f(u[c + 7]));
-    }
-    x0 = max3(x0, as_f(u[60]), as_f(u[61]));
-    x1 = max3(x1, as_f(u[62]), as_f(u[63]));
-    return fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
-}
-
-// The smallest bf16 at or above x, as the 16 high bits of its f32 pattern (-inf stays -inf).
-FV_DEV uint16_t bf16_ceil(float x) {
-    uint32_t b = as_u(x);
-    if (x > 0.f && (b & 0xffffu)) b += 0x10000u;  // positive: truncation rounds down, step up
-    return (uint16_t)(b >> 16);                    // negative: truncation already rounds toward zero, i.e. up
-}
-FV_DEV float bf16_bits_to_f(uint16_t h) { return as_f((uint32_t)h << 16); }
-
 // Bounded wait on phase `parity` of a CTA barrier.  What it needs to give up cleanly (abort flag in
 // shared memory, status word and cycle budget in the kernel's parameters) is fetched on the slow path
-// only, so a role keeps no wait state in registers.  False after a timeout, or when another thread of
-// the CTA has given up.
+// only, so a role keeps no wait state in registers.  Every probe of a barrier is a shared-memory access
+// that competes with the operand reads of the MMAs in flight -- a tight two-instruction spin in the ten
+// waiting warps cost 13 % of the kernel -- so a waiter backs off between probes (FV_ATT_BACKOFF ns).
+// False after a timeout, or when another thread of the CTA has given up.
 struct Waiter {
     const Job& jb;
     uint32_t sbase;
@@ -287,6 +310,9 @@ struct Waiter {
         const long long t0 = clock64();
         uint32_t n = 0;
         while (!mbar_try(bar, parity)) {
+#if FV_ATT_BACKOFF > 0
+            __nanosleep(FV_ATT_BACKOFF);
+#endif
             if (((++n) & 63u) == 0u) {
                 uint32_t gone;
                 asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(gone) : "r"(sbase + Smem::abort_flag) : "memory");
@@ -302,21 +328,167 @@ struct Waiter {
     }
 };
 
-FV_DEV void sts_u16(uint32_t addr, uint16_t v) {
-    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
-}
-FV_DEV uint16_t lds_u16(uint32_t addr) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
-    return v;
+// One arrival for the whole warp: every lane has finished what the barrier publishes (TMEM stores
+// followed by tcgen05.wait::st and fence::before_thread_sync), the warp meets, one lane arrives.
+FV_DEV void warp_arrive(uint32_t bar, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
 }
 
-// One phase of the 64-thread barrier of a row's two warps.
-FV_DEV bool pair_sync(uint32_t bar, uint32_t& count, const Waiter& wait) {
-    mbar_arrive(bar);
-    const bool ok = wait(bar, count & 1u);
-    count++;
-    return ok;
+// 2^(u * sl2 + noff) for 32 score columns: packed bf16 pairs into pw[0 .. 15]; the f32 values are
+// added into the two packed accumulators.  POLY: every FV_ATT_POLY-th pair goes through the FMA-pipe
+// exponential (fvp::ex2_poly_x2) instead of MUFU; only for tiles without masked columns, because the
+// polynomial never returns an exact zero.  The polynomial wraps around above 2^127 instead of giving
+// inf, which the caller's sum guard could not see: the largest argument given to it is kept in `top`
+// (one three-input max per pair) and checked with the sum.
+template <bool POLY>
+FV_DEV void exp32(const uint32_t (&u)[32], uint32_t* pw, uint64_t s2, uint64_t nf, uint64_t& acc0, uint64_t& acc1, float& top) {
+#pragma unroll
+    for (int w = 0; w < 16; w++) {
+        float t0, t1, p0, p1;
+        unpack_f32x2(fma_f32x2(pack_f32x2(as_f(u[2 * w]), as_f(u[2 * w + 1])), s2, nf), t0, t1);
+        if (POLY && FV_ATT_POLY > 0 && (w % FV_ATT_POLY) == FV_ATT_POLY - 1) {
+            top = max3(top, t0, t1);
+            ex2_poly_x2(t0, t1, p0, p1);
+        } else {
+            p0 = ex2(t0);
+            p1 = ex2(t1);
+        }
+        const uint64_t pp = pack_f32x2(p0, p1);
+        if (w & 1) acc1 = add_f32x2(acc1, pp);
+        else acc0 = add_f32x2(acc0, pp);
+        pw[w] = pack_bf16x2(p0, p1);
+    }
+}
+
+FV_DEV float max32(const uint32_t (&u)[32]) {
+    float x0 = max3(as_f(u[0]), as_f(u[1]), as_f(u[2])), x1 = max3(as_f(u[3]), as_f(u[4]), as_f(u[5]));
+    float x2 = max3(as_f(u[6]), as_f(u[7]), as_f(u[8])), x3 = max3(as_f(u[9]), as_f(u[10]), as_f(u[11]));
+#pragma unroll
+    for (int c = 12; c < 28; c += 8) {
+        x0 = max3(x0, as_f(u[c]), as_f(u[c + 1]));
+        x1 = max3(x1, as_f(u[c + 2]), as_f(u[c + 3]));
+        x2 = max3(x2, as_f(u[c + 4]), as_f(u[c + 5]));
+        x3 = max3(x3, as_f(u[c + 6]), as_f(u[c + 7]));
+    }
+    x0 = max3(x0, as_f(u[28]), as_f(u[29]));
+    x1 = max3(x1, as_f(u[30]), as_f(u[31]));
+    return fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
+}
+
+// Columns of one row of a key tile that the row may see: [lo, hi) U [0, sink), tile-relative.
+struct Cols {
+    int lo, hi, sink;
+    bool whole;  // every one of the 128 columns is visible
+    template <int C0>
+    FV_DEV void hide(uint32_t (&x)[32]) const {  // columns C0 .. C0 + 31: the invisible ones become -inf
+        if (whole) return;
+#pragma unroll
+        for (int c = 0; c < 32; c++) {
+            const bool vis = (C0 + c >= lo && C0 + c < hi) || C0 + c < sink;
+            x[c] = vis ? x[c] : as_u(neg_inf());
+        }
+    }
+};
+
+// Exponentials of one half (64 columns) of this thread's row of S out of two 32-column register arrays
+// whose TMEM loads have completed: P = 2^(s * sl2 + noff) as 32 packed words, returns the half row's sum.
+template <bool POLY>
+FV_DEV float half_exp(const uint32_t (&ua)[32], const uint32_t (&ub)[32], float sl2, float noff, uint32_t (&pw)[32]) {
+    uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
+    const uint64_t s2 = pack_f32x2(sl2, sl2), nf = pack_f32x2(noff, noff);
+    float top = 0.f;
+    exp32<POLY>(ua, pw, s2, nf, acc0, acc1, top);
+    exp32<POLY>(ub, pw + 16, s2, nf, acc0, acc1, top);
+    float a, b, c, d;
+    unpack_f32x2(acc0, a, b);
+    unpack_f32x2(acc1, c, d);
+    const float sum = (a + b) + (c + d);
+    // (an argument the polynomial cannot take makes the half row's sum infinite: the guard sends the tile the careful way)
+    return (POLY && top > 120.f) ? __int_as_float(0x7f800000) : sum;
+}
+FV_DEV void load_half(uint32_t tS_half, uint32_t (&ua)[32], uint32_t (&ub)[32]) {
+    tmem_ld32_issue(tS_half, ua);
+    tmem_ld32_issue(tS_half + 32u, ub);
+}
+FV_DEV void land_half(uint32_t (&ua)[32], uint32_t (&ub)[32]) {
+    tmem_ld_wait();
+    tmem_pin(ua);
+    tmem_pin(ub);
+}
+// P of 64 keys into TMEM at column `col` of the row's score block, then the warp's arrival at `bar`.
+FV_DEV void hand_over(uint32_t tS, uint32_t col, const uint32_t (&pw)[32], uint32_t bar, int lane) {
+    tmem_st32(tS + col, pw);
+    tmem_st_wait();
+    tc_fence_before();
+    warp_arrive(bar, lane);
+}
+
+// What a row carries from key tile to key tile.
+struct RowState {
+    float m, l;  // reference (base-2 domain, -inf = none yet) and sum of P against it
+};
+
+// The careful way through one key tile (or through its second half): masks honoured, exact row maxima
+// first, the reference moved where it is missing or more than 2^8 behind, O and the row sum brought
+// to the new reference, P evaluated on the MUFU path (an invisible column gives an exact zero).  Kept
+// OUT OF LINE on purpose: it runs on the first tile of an item, on tiles a mask cuts through, on a
+// segment's last partial tile and when a guard trips, and inlined it more than doubled the code the
+// hot loop is spread over (instruction-fetch stalls tripled).
+//   second_only: the first half of P is already with the issuer (stored against the old reference);
+//   its product must have finished before O is touched -- the caller has waited for pv_early.
+//   have_o: O holds products of this item (earlier tiles, or this tile's first half).
+__device__ __noinline__ void careful_tile(uint32_t tS, uint32_t tO, uint32_t bt, Cols cols, float sl2, bool second_only,
+                                          bool have_o, int lane, RowState* rs) {
+    float m = rs->m, l = rs->l;
+    uint32_t ua[32], ub[32];
+    float mx = neg_inf();
+    if (!second_only) {
+        load_half(tS, ua, ub);
+        land_half(ua, ub);
+        cols.hide<0>(ua);
+        cols.hide<32>(ub);
+        mx = fmaxf(max32(ua), max32(ub));
+    }
+    load_half(tS + 64u, ua, ub);
+    land_half(ua, ub);
+    cols.hide<64>(ua);
+    cols.hide<96>(ub);
+    mx = fmaxf(mx, fmaxf(max32(ua), max32(ub)));
+    const float cand = mx * sl2;
+    float a = 1.f;
+    if (cand > m + 8.f) {   // (-inf + 8 = -inf: any finite maximum replaces a missing reference)
+        a = ex2(m - cand);  // 0 when there was none
+        m = cand;
+        l *= a;
+    }
+    if (have_o && __any_sync(kFullWarp, a != 1.f)) {
+#pragma unroll 1
+        for (int q = 0; q < 4; q++) {
+            uint32_t o[32];
+            tmem_ld32_issue(tO + 32u * q, o);
+            tmem_ld_wait();
+            tmem_pin(o);
+#pragma unroll
+            for (int c = 0; c < 32; c++) o[c] = as_u(as_f(o[c]) * a);
+            tmem_st32(tO + 32u * q, o);
+        }
+    }
+    const float noff = (m == neg_inf()) ? 0.f : -m;  // a row that still sees nothing: P = 2^-inf = 0
+    uint32_t pw[32];
+    if (!second_only) {
+        uint32_t uc[32], ud[32];
+        load_half(tS, uc, ud);
+        land_half(uc, ud);
+        cols.hide<0>(uc);
+        cols.hide<32>(ud);
+        l += half_exp<false>(uc, ud, sl2, noff, pw);
+        hand_over(tS, 0u, pw, bt + Smem::p_early, lane);
+    }
+    l += half_exp<false>(ua, ub, sl2, noff, pw);  // (ua, ub still hold the masked scores of the second half)
+    hand_over(tS, 32u, pw, bt + Smem::p_ready, lane);
+    rs->m = m;
+    rs->l = l;
 }
 
 // 32 columns of one output row: O / l (+ the earlier pass' share), to bf16 or f32.
@@ -350,27 +522,23 @@ FV_DEV void store_cols32(const Job& jb, const uint32_t (&o)[32], float inv, floa
 }
 
 template <bool MASKED>
-FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp, int lane,
-                         const Waiter& wait) {
-    const int tile = warp >> 3, half = (warp >> 2) & 1, quad = warp & 3;
+FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp, int lane, const Waiter& wait) {
+    const int tile = warp >> 2, quad = warp & 3;
     const int row = quad * 32 + lane;
     const uint32_t lanes = tmem + ((uint32_t)(quad * 32) << 16);
-    const uint32_t tS = lanes + 256u * (uint32_t)tile + 64u * (uint32_t)half;          // this thread's 64 score columns
-    const uint32_t tO = tS + 128u;                                                      // its 64 output columns
-    const uint32_t bt = sbase + 8u * (uint32_t)tile;  // + Smem::{s_ready, p_early, p_ready, o_ready}: this row tile's barriers
-    const uint32_t b_pair = sbase + Smem::pair + 8u * (uint32_t)(tile * 4 + quad);
-    // exchange words of this row: u16 [parity 2] 512 bytes apart; the other half's are 256 bytes away
-    const uint32_t mine = sbase + Smem::xch + 2u * (uint32_t)(tile * 512 + half * 128 + row);
-    const uint32_t theirs = sbase + Smem::xch + 2u * (uint32_t)(tile * 512 + (1 - half) * 128 + row);
+    const uint32_t tS = lanes + tmem_scores((uint32_t)tile);  // this row's scores (and P)
+    const uint32_t tO = lanes + tmem_output((uint32_t)tile);  // its output accumulator
+    const uint32_t bt = sbase + 8u * (uint32_t)tile;  // + Smem::{s_ready, p_early, p_ready, pv_early, o_ready}: this row tile's barriers
     const float sl2 = jb.sl2;
-    uint32_t s_count = 0, o_count = 0, x_count = 0;
+    uint32_t s_count = 0, o_count = 0;
 
-    for (int i = (int)blockIdx.x; i < jb.items; i += (int)gridDim.x) {
+    Deal deal;
+    for (int i = deal.next(jb); i >= 0; i = deal.next(jb)) {
         const Item it = item_at(jb, i);
         const int qr = it.q0 + kRowTile * tile + row;  // this thread's row inside the plane
         const Span cta_span = span_of<MASKED>(jb, global_row(jb, it.q0), global_row(jb, min(it.q0 + kItemRows, jb.sq) - 1));
         const Span row_span = span_of<MASKED>(jb, global_row(jb, qr), global_row(jb, qr));
-        float m = neg_inf(), l = 0.f;
+        RowState rs{neg_inf(), 0.f};
         int seen = 0;
         KeyWalk<MASKED> walk;
         KeyTile kt;
@@ -379,77 +547,45 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
             if (!__all_sync(kFullWarp, wait(bt + Smem::s_ready, s_count & 1u))) return;
             s_count++;
             tc_fence_after();
-            uint32_t u[64];
-            tmem_ld32_at<0>(tS, u);
-            tmem_ld32_at<32>(tS + 32u, u);
-            tmem_ld_wait();
-            tmem_pin(u);
 
-            // columns of this half the row may not see become -inf
-            const int kb = kt.k0 + 64 * half;
-            const int nv = min(max(kt.valid - 64 * half, 0), 64);
-            bool whole;
+            Cols cols{0, kt.valid, 0, kt.valid == kKeyTile};
             if constexpr (MASKED) {
-                const int c_lo = row_span.lo - kb, c_hi = min(row_span.hi - kb, nv), c_sink = min(row_span.sink - kb, nv);
-                whole = (c_lo <= 0 && c_hi >= 64) || c_sink >= 64;
-                if (!whole) {
-#pragma unroll
-                    for (int c = 0; c < 64; c++) {
-                        const bool vis = (c >= c_lo && c < c_hi) || c < c_sink;
-                        u[c] = vis ? u[c] : as_u(neg_inf());
+                cols.lo = row_span.lo - kt.k0;
+                cols.hi = min(row_span.hi - kt.k0, kt.valid);
+                cols.sink = min(row_span.sink - kt.k0, kt.valid);
+                cols.whole = (cols.lo <= 0 && cols.hi >= kKeyTile) || cols.sink >= kKeyTile;
+            }
+            // The hot path takes whole tiles of rows that all have a reference (warp-uniform choice:
+            // everything below is warp-collective); the rest goes the careful way.
+            bool hot = seen > 0 && __all_sync(kFullWarp, cols.whole && rs.m != neg_inf());
+            if (hot) {
+                uint32_t ua[32], ub[32], pw[32];
+                load_half(tS, ua, ub);
+                land_half(ua, ub);
+                const float sum0 = half_exp<true>(ua, ub, sl2, -rs.m, pw);
+                load_half(tS + 64u, ua, ub);  // on its way while the first half is handed over
+                if (__any_sync(kFullWarp, !(sum0 <= kGuard))) {
+                    land_half(ua, ub);        // (nothing may be in flight into registers when the call is made)
+                    hot = false;              // nothing of this tile is stored: the careful way, whole tile
+                } else {
+                    hand_over(tS, 0u, pw, bt + Smem::p_early, lane);
+                    land_half(ua, ub);
+                    const float sum1 = half_exp<true>(ua, ub, sl2, -rs.m, pw);
+                    if (__any_sync(kFullWarp, !(sum1 <= kGuard))) {
+                        // The first half went out against the old reference and its product may be running:
+                        // wait for it (the issuer signals every early product), then the careful way for the
+                        // second half, whose scores (columns 64-127 of S) are untouched.
+                        rs.l += sum0;
+                        if (!__all_sync(kFullWarp, wait(bt + Smem::pv_early, (s_count - 1u) & 1u))) return;
+                        tc_fence_after();
+                        careful_tile(tS, tO, bt, cols, sl2, true, true, lane, &rs);
+                    } else {
+                        hand_over(tS, 32u, pw, bt + Smem::p_ready, lane);
+                        rs.l += sum0 + sum1;
                     }
                 }
-            } else {
-                whole = nv == 64;
-                if (!whole) {
-#pragma unroll
-                    for (int c = 0; c < 64; c++) u[c] = c < nv ? u[c] : as_u(neg_inf());
-                }
             }
-
-            // the two halves of the row agree on the tile's maximum
-            const uint16_t mine_up = bf16_ceil(max64(u));
-            const uint32_t par = x_count & 1u;
-            sts_u16(mine + 512u * par, mine_up);
-            if (!__all_sync(kFullWarp, pair_sync(b_pair, x_count, wait))) return;
-            const float cand = fmaxf(bf16_bits_to_f(mine_up), bf16_bits_to_f(lds_u16(theirs + 512u * par))) * sl2;
-            const bool grow = cand > m + kSlackLog2;
-            float a = 1.f;
-            if (grow) {
-                a = ex2(m - cand);
-                m = cand;
-                l *= a;
-            }
-            // O holds P.V of the earlier tiles of the item (those MMAs were issued before the one that
-            // produced this S, and S is complete): rescale this thread's 64 columns when a reference moved.
-            if (seen > 0 && __any_sync(kFullWarp, grow)) {
-#pragma unroll 1
-                for (int q = 0; q < 2; q++) {
-                    uint32_t o[32];
-                    tmem_ld32_issue(tO + 32u * q, o);
-                    tmem_ld_wait();
-                    tmem_pin(o);
-#pragma unroll
-                    for (int c = 0; c < 32; c++) o[c] = as_u(as_f(o[c]) * a);
-                    tmem_st32(tO + 32u * q, o);
-                }
-            }
-            const float noff = (m == neg_inf()) ? 0.f : -m;
-            uint32_t pw[32];
-            float sum;
-            // (warp-uniform choice: the TMEM stores are warp-collective)
-            const bool poly = __all_sync(kFullWarp, whole);
-            sum = poly ? exp_chunk<0, true>(u, pw, sl2, noff) : exp_chunk<0, false>(u, pw, sl2, noff);
-            tmem_st16_at<0>(tS, pw);
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(bt + Smem::p_early);
-            sum += poly ? exp_chunk<32, true>(u, pw, sl2, noff) : exp_chunk<32, false>(u, pw, sl2, noff);
-            tmem_st16_at<16>(tS + 16u, pw);
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(bt + Smem::p_ready);
-            l += sum;
+            if (!hot) careful_tile(tS, tO, bt, cols, sl2, false, seen > 0, lane, &rs);
             seen++;
         }
 
@@ -459,20 +595,10 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
             o_count++;
             tc_fence_after();
         }
-        // Row sum = this half's + the other half's.  First phase: the partner has read this item's last
-        // maximum out of the exchange words; second: both sums are written; third: both are read.
-        if (!__all_sync(kFullWarp, pair_sync(b_pair, x_count, wait))) return;
-        const uint32_t lbits = as_u(l);
-        sts_u16(mine, (uint16_t)(lbits & 0xffffu));
-        sts_u16(mine + 512u, (uint16_t)(lbits >> 16));
-        if (!__all_sync(kFullWarp, pair_sync(b_pair, x_count, wait))) return;
-        const float l_other = as_f((uint32_t)lds_u16(theirs) | ((uint32_t)lds_u16(theirs + 512u) << 16));
-        if (!__all_sync(kFullWarp, pair_sync(b_pair, x_count, wait))) return;
-        const float lsum = l + l_other;
-
         const bool live = qr < jb.sq;  // rows past sq only take part in the warp-collective TMEM loads
-        float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-        const float lse = lsum > 0.f ? m + log2f(lsum) : neg_inf();
+        const float m = rs.m, l = rs.l;
+        float inv = l > 0.f ? 1.f / l : 0.f;
+        const float lse = l > 0.f ? m + log2f(l) : neg_inf();
         const size_t rowi = (size_t)it.plane * jb.sq + (live ? qr : 0);
         float prev_w = 0.f;
         if (live) {
@@ -487,8 +613,8 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
                     prev_w = wp * den;
                     lse_all = top + log2f(wn + wp);
                 }
-                if (jb.lse_out && half == 0) jb.lse_out[rowi] = lse_all;
-            } else if (jb.lse_out && half == 0) {
+                if (jb.lse_out) jb.lse_out[rowi] = lse_all;
+            } else if (jb.lse_out) {
                 jb.lse_out[rowi] = lse;
             }
         }
@@ -499,7 +625,7 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
             out_el = (((size_t)bb * jb.sq + (live ? qr : 0)) * jb.out_heads + hh) * kD;
         }
 #pragma unroll 1
-        for (int q = 0; q < 2; q++) {
+        for (int q = 0; q < 4; q++) {
             uint32_t o[32];
             if (seen > 0) {  // warp-uniform
                 tmem_ld32_issue(tO + 32u * q, o);
@@ -510,13 +636,12 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
                 for (int c = 0; c < 32; c++) o[c] = 0u;
             }
             if (!live) continue;
-            const int col = 64 * half + 32 * q;
-            void* dst = jb.out_is_bf16 ? (void*)(reinterpret_cast<unsigned short*>(jb.out) + out_el + col)
-                                       : (void*)(reinterpret_cast<float*>(jb.out) + out_el + col);
-            store_cols32(jb, o, inv, prev_w, jb.prev_o ? jb.prev_o + prev_el + col : nullptr, dst);
+            void* dst = jb.out_is_bf16 ? (void*)(reinterpret_cast<unsigned short*>(jb.out) + out_el + 32 * q)
+                                       : (void*)(reinterpret_cast<float*>(jb.out) + out_el + 32 * q);
+            store_cols32(jb, o, inv, prev_w, jb.prev_o ? jb.prev_o + prev_el + 32 * q : nullptr, dst);
         }
-        // The next item's first P.V overwrites O.  The issuer issues it only after all 256 threads of the
-        // row tile have arrived at p_ready for that item's first key tile, and a thread gets there only
+        // The next item's first P.V overwrites O.  The issuer issues it only after all four warps of the
+        // row tile have arrived at p_ready for that item's first key tile, and a warp gets there only
         // after its loads above have completed.
     }
 }
@@ -553,20 +678,21 @@ FV_DEV void loader_thread(const CUtensorMap* mq, const CUtensorMap* mk, const CU
         return true;
     };
 
-    int i = (int)blockIdx.x;
+    Deal deal;
+    int i = deal.next(jb);
     bool ok = true;
-    if (i < jb.items) ok = load_q(i, 0) && load_q(i, 1);
-    for (; ok && i < jb.items; i += (int)gridDim.x) {
-        const int nxt = i + (int)gridDim.x;
+    if (i >= 0) ok = load_q(i, 0) && load_q(i, 1);
+    for (; ok && i >= 0; i = deal.next(jb)) {
+        const int nxt = deal.peek(jb);
         // Row tile A of the next item goes into the slot the previous item's tile B left long ago.
-        if (nxt < jb.items) ok = load_q(nxt, 0);
+        if (nxt >= 0) ok = load_q(nxt, 0);
         const Item it = item_at(jb, i);
         const Span sp = span_of<MASKED>(jb, global_row(jb, it.q0), global_row(jb, min(it.q0 + kItemRows, jb.sq) - 1));
         KeyWalk<MASKED> walk;
         KeyTile kt;
         while (ok && walk.next(jb, sp, kt)) ok = load_kv(mk, kt, it.plane) && load_kv(mv, kt, it.plane);
         // Tile B of the next item takes the slot of this item's tile A, free after its last Q.K^T.
-        if (ok && nxt < jb.items) ok = load_q(nxt, 1);
+        if (ok && nxt >= 0) ok = load_q(nxt, 1);
     }
     // Copies in flight must land before the CTA's shared memory goes away.  After a clean run the
     // issuer has waited on every one of these phases already and the loops fall straight through.
@@ -581,102 +707,93 @@ FV_DEV void loader_thread(const CUtensorMap* mq, const CUtensorMap* mk, const CU
 }
 
 // --------------------------------------------------------------------------------------- issuer
-// P_t(j) . V(j) into O_t.  The first product of an item overwrites O, which the softmax threads of
-// the previous item may still be reading until every one of them has stored the whole of this tile's
-// P: that product waits for p_ready first; later ones start on the early half.
-FV_DEV bool issue_output(uint32_t sbase, int t, uint32_t tmem, uint32_t v_smem, bool fresh, uint32_t& p_count,
+// Ring positions are plain counters: load number c lives in slot c % slots, and it is the
+// (c / slots)-th use of that slot, whose barrier phase has the parity of that quotient.
+FV_DEV uint32_t kv_slot_addr(uint32_t sbase, uint32_t c) { return sbase + Smem::kv + (c % kKvSlots) * kSlotBytes; }
+
+// P_t(j) . V(j) into O_t in two steps, keys 0-63 as soon as that half of P is stored, then the rest.
+// `pc` counts the P tiles of this row tile consumed so far (its parity is the phase of p_early,
+// p_ready and pv_early).  The first product of an item overwrites O; the softmax threads of the
+// previous item have finished reading it by the time they have stored any of the new item's P.
+// (An issuer that serves the two row tiles out of order, probing their barriers without blocking, was
+// tried: its probes compete with the MMAs' operand reads for shared memory and it ran 23 % slower.)
+FV_DEV bool issue_output(uint32_t sbase, uint32_t t, uint32_t tmem, uint64_t vd, bool fresh, uint32_t pc,
                          const Waiter& wait) {
-    const uint32_t tS = tmem + 256u * (uint32_t)t, tO = tS + 128u;
-    const uint32_t b_pe = sbase + Smem::p_early + 8u * t, b_pr = sbase + Smem::p_ready + 8u * t;
-    const uint32_t par = p_count & 1u;
-    p_count++;
-    if (fresh) {
-        if (!wait(b_pe, par) || !wait(b_pr, par)) return false;
-        tc_fence_after();
-        output_mma<0xffu>(tO, tS, v_smem, true);
-        return true;
-    }
-    if (!wait(b_pe, par)) return false;
+    const uint32_t bt = sbase + 8u * t, tO = tmem + tmem_output(t), tP = tmem + tmem_scores(t);
+    if (!wait(bt + Smem::p_early, pc & 1u)) return false;
     tc_fence_after();
-    output_mma<0x33u>(tO, tS, v_smem, false);  // keys 0-31 and 64-95
-    if (!wait(b_pr, par)) return false;
+    output_mma_early(tO, tP, vd, fresh);
+    umma_commit(bt + Smem::pv_early);
+    if (!wait(bt + Smem::p_ready, pc & 1u)) return false;
     tc_fence_after();
-    output_mma<0xccu>(tO, tS, v_smem, false);  // keys 32-63 and 96-127
+    output_mma_late(tO, tP, vd);
     return true;
 }
 
 template <bool MASKED>
 FV_DEV void issuer_thread(const Job& jb, uint32_t sbase, uint32_t tmem, const Waiter& wait) {
-    uint32_t qn = 0, kvn = 0;
-    uint32_t p_count[2] = {0u, 0u};
-    bool ok = true;
-    for (int i = (int)blockIdx.x; ok && i < jb.items; i += (int)gridDim.x) {
+    uint32_t qn = 0;   // Q tiles consumed (two per item)
+    uint32_t kc = 0;   // K/V tiles consumed
+    uint32_t pc = 0;   // P tiles consumed per row tile
+    Deal deal;
+    for (int i = deal.next(jb); i >= 0; i = deal.next(jb)) {
         const Item it = item_at(jb, i);
         const Span sp = span_of<MASKED>(jb, global_row(jb, it.q0), global_row(jb, min(it.q0 + kItemRows, jb.sq) - 1));
         const int n = count_tiles<MASKED>(jb, sp);
-        uint32_t q_slot[2], q_smem[2], q_par[2];
-#pragma unroll
-        for (int t = 0; t < 2; t++) {
-            q_slot[t] = (qn + t) % kQSlots;
-            q_par[t] = ((qn + t) / kQSlots) & 1u;
-            q_smem[t] = sbase + Smem::q + q_slot[t] * kSlotBytes;
-        }
+        const uint32_t qa = qn % kQSlots, qb = (qn + 1u) % kQSlots;  // this item's Q slots
+        const uint32_t qa_par = (qn / kQSlots) & 1u, qb_par = ((qn + 1u) / kQSlots) & 1u;
         qn += 2;
         if (n == 0) {
             // No key of any segment is visible to these rows.  The Q tiles were loaded all the same: let
             // them land before their slots are handed back.
-#pragma unroll
-            for (int t = 0; t < 2; t++) {
-                if (ok && !wait(sbase + Smem::q_full + 8u * q_slot[t], q_par[t])) ok = false;
-                if (ok) mbar_arrive(sbase + Smem::q_free + 8u * q_slot[t]);
-            }
+            if (!wait(sbase + Smem::q_full + 8u * qa, qa_par) || !wait(sbase + Smem::q_full + 8u * qb, qb_par)) break;
+            mbar_arrive(sbase + Smem::q_free + 8u * qa);
+            mbar_arrive(sbase + Smem::q_free + 8u * qb);
             continue;
         }
-        for (int j = 0; ok && j < n; j++) {
-            const uint32_t ik = kvn + 2u * (uint32_t)j, k_slot = ik % kKvSlots;
-            const uint32_t k_smem = sbase + Smem::kv + k_slot * kSlotBytes;
-            uint32_t v_slot = 0, v_smem = 0;
+        const uint64_t qd_a = umma_desc_sw128(sbase + Smem::q + qa * kSlotBytes, 16, 1024);
+        const uint64_t qd_b = umma_desc_sw128(sbase + Smem::q + qb * kSlotBytes, 16, 1024);
+        bool ok = true;
+#pragma unroll 1
+        for (int j = 0; j <= n; j++) {
+            // step j: O_t += P_t(j-1) . V(j-1) for j > 0, then S_t = Q_t . K(j)^T for j < n; t = A, B
+            uint64_t vd = 0, kd = 0;
             if (j > 0) {  // V(j-1) was loaded before K(j): the products that need it go first
-                const uint32_t iv = ik - 1u;
-                v_slot = iv % kKvSlots;
-                if (!wait(sbase + Smem::kv_full + 8u * v_slot, (iv / kKvSlots) & 1u)) { ok = false; break; }
-                v_smem = sbase + Smem::kv + v_slot * kSlotBytes;
+                if (!wait(sbase + Smem::kv_full + 8u * ((kc - 1u) % kKvSlots), ((kc - 1u) / kKvSlots) & 1u)) { ok = false; break; }
+                vd = umma_desc_sw128(kv_slot_addr(sbase, kc - 1u), kPanelBytes, 1024);
                 tc_fence_after();
             }
+            if (j < n) kd = umma_desc_sw128(kv_slot_addr(sbase, kc), 16, 1024);
 #pragma unroll
-            for (int t = 0; t < 2; t++) {
-                if (j > 0 && ok) ok = issue_output(sbase, t, tmem, v_smem, j == 1, p_count[t], wait);
-                if (t == 0 && ok) {
-                    if (!wait(sbase + Smem::kv_full + 8u * k_slot, (ik / kKvSlots) & 1u)) ok = false;
+            for (uint32_t t = 0; t < 2; t++) {
+                if (j > 0 && !issue_output(sbase, t, tmem, vd, j == 1, pc, wait)) { ok = false; break; }
+                if (j == n) {
+                    umma_commit(sbase + Smem::o_ready + 8u * t);
+                    continue;
+                }
+                if (t == 0) {
+                    if (!wait(sbase + Smem::kv_full + 8u * (kc % kKvSlots), (kc / kKvSlots) & 1u)) { ok = false; break; }
                     tc_fence_after();
                 }
-                // (tile B of an item is loaded late, see loader_thread: it is waited for where it is first used)
-                if (j == 0 && ok && !wait(sbase + Smem::q_full + 8u * q_slot[t], q_par[t])) ok = false;
-                if (!ok) break;
-                if (j == 0) tc_fence_after();
-                scores_mma(tmem + 256u * (uint32_t)t, q_smem[t], k_smem);
+                if (j == 0) {  // (tile B of an item is loaded late, see loader_thread: it is waited for where it is first used)
+                    if (!wait(sbase + Smem::q_full + 8u * (t ? qb : qa), t ? qb_par : qa_par)) { ok = false; break; }
+                    tc_fence_after();
+                }
+                scores_mma(tmem + tmem_scores(t), t ? qd_b : qd_a, kd);
                 umma_commit(sbase + Smem::s_ready + 8u * t);
-                if (j == n - 1) umma_commit(sbase + Smem::q_free + 8u * q_slot[t]);
+                if (j == n - 1) umma_commit(sbase + Smem::q_free + 8u * (t ? qb : qa));
             }
             if (!ok) break;
-            if (j > 0) umma_commit(sbase + Smem::kv_free + 8u * v_slot);
-            umma_commit(sbase + Smem::kv_free + 8u * k_slot);
+            if (j > 0) {
+                umma_commit(sbase + Smem::kv_free + 8u * ((kc - 1u) % kKvSlots));
+                pc++;
+            }
+            if (j < n) {
+                umma_commit(sbase + Smem::kv_free + 8u * (kc % kKvSlots));
+                kc += 2;   // K(j) and, next step, V(j)
+            }
         }
         if (!ok) break;
-        {   // the last key tile's P.V
-            const uint32_t iv = kvn + 2u * (uint32_t)n - 1u, v_slot = iv % kKvSlots;
-            if (!wait(sbase + Smem::kv_full + 8u * v_slot, (iv / kKvSlots) & 1u)) break;
-            tc_fence_after();
-            const uint32_t v_smem = sbase + Smem::kv + v_slot * kSlotBytes;
-#pragma unroll
-            for (int t = 0; t < 2; t++) {
-                if (ok) ok = issue_output(sbase, t, tmem, v_smem, n == 1, p_count[t], wait);
-                if (ok) umma_commit(sbase + Smem::o_ready + 8u * t);
-            }
-            if (!ok) break;
-            umma_commit(sbase + Smem::kv_free + 8u * v_slot);
-        }
-        kvn += 2u * (uint32_t)n;
     }
     // Nothing this thread issued may still be running when TMEM is freed.
     umma_commit(sbase + Smem::drain);
@@ -703,11 +820,11 @@ FV_DEV void attn_persistent(const CUtensorMap* mq, const CUtensorMap* mk, const 
         }
         for (int t = 0; t < 2; t++) {
             mbar_init(sbase + Smem::s_ready + 8u * t, 1);
-            mbar_init(sbase + Smem::p_early + 8u * t, 256);
-            mbar_init(sbase + Smem::p_ready + 8u * t, 256);
+            mbar_init(sbase + Smem::p_early + 8u * t, 4);  // the row tile's four softmax warps
+            mbar_init(sbase + Smem::p_ready + 8u * t, 4);
+            mbar_init(sbase + Smem::pv_early + 8u * t, 1);
             mbar_init(sbase + Smem::o_ready + 8u * t, 1);
         }
-        for (int p = 0; p < 8; p++) mbar_init(sbase + Smem::pair + 8u * p, 64);
         mbar_init(sbase + Smem::drain, 1);
         // A CTA that starts after another one gave up does nothing.
         int bad = (*(volatile int*)jb.status != FV_ST_OK) ? 1 : 0;
@@ -727,11 +844,11 @@ FV_DEV void attn_persistent(const CUtensorMap* mq, const CUtensorMap* mk, const 
     const uint32_t tmem = *tmem_slot;
 
     if (warp < kSoftmaxWarps) {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 104;" ::: "memory");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;" ::: "memory");
         softmax_warp<MASKED>(jb, sbase, tmem, warp, lane, Waiter{jb, sbase, 3});
     } else {
-        // (one setmaxnreg for the whole warpgroup: warps 16-19 execute this very instruction together)
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
+        // (one setmaxnreg for the whole warpgroup: warps 8-11 execute this very instruction together)
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
         if (lane == 0) {
             if (warp == kLoaderWarp) loader_thread<MASKED>(mq, mk, mv, jb, sbase, Waiter{jb, sbase, 1});
             else if (warp == kIssuerWarp) issuer_thread<MASKED>(jb, sbase, tmem, Waiter{jb, sbase, 2});

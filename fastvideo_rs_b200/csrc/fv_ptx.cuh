@@ -48,6 +48,19 @@ FV_DEV uint32_t mbar_try(uint32_t bar, uint32_t parity) {
     return ok;
 }
 
+// Non-blocking probe of phase `parity` (test_wait never suspends the thread).
+FV_DEV uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
 // What a role needs to give up cleanly: the CTA's abort flag (shared) and the
 // launch's status word (global).
 struct WaitCtl {
@@ -195,10 +208,15 @@ FV_DEV void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], " FV_L32_B ";" ::"r"(taddr), FV_I32(r, 0) : "memory");
 }
 
-// Store 16 registers r[OFF .. OFF+15] to 16 consecutive TMEM columns of this thread's lane.
+// Store r[OFF .. OFF+31] to 32 consecutive TMEM columns of this thread's lane.
 template <int OFF, int N>
-FV_DEV void tmem_st16_at(uint32_t taddr, const uint32_t (&r)[N]) {
-    static_assert(OFF + 16 <= N, "tmem_st16_at: out of range");
+FV_DEV void tmem_st32_at(uint32_t taddr, const uint32_t (&r)[N]) {
+    static_assert(OFF + 32 <= N, "tmem_st32_at: out of range");
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], " FV_L32_B ";" ::"r"(taddr), FV_I32(r, OFF) : "memory");
+}
+// Store 16 registers to 16 consecutive TMEM columns of this thread's lane.
+FV_DEV void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    constexpr int OFF = 0;
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
         ::"r"(taddr), FV_I16(r, OFF)

@@ -50,8 +50,9 @@ def _i32(vals):
 
 
 def segments_fwd(q, k_all, v_all, seg_len, seg_start, seg_rows, scale, *, out=None, out_bf16=True, causal=None,
-                 q_row0=0, lse_out=None, prev_o=None, prev_lse=None):
-    """fv_sdpa_segments_bf16: q [bh, sq, 128]; k_all / v_all [nseg, bh, seg_rows, 128]."""
+                 q_row0=0, q_split=0, q_row1=0, lse_out=None, prev_o=None, prev_lse=None):
+    """fv_sdpa_segments_runs_bf16: q [bh, sq, 128]; k_all / v_all [nseg, bh, seg_rows, 128].  Rows from q_split on
+    (when > 0) are a second run of the sequence starting at global row q_row1."""
     bh, sq, d = q.shape
     nseg = len(seg_len)
     if out is None:
@@ -60,212 +61,262 @@ def segments_fwd(q, k_all, v_all, seg_len, seg_start, seg_rows, scale, *, out=No
     vp = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
     fp = lambda t: ctypes.cast(ctypes.c_void_p(t.data_ptr()), ctypes.POINTER(ctypes.c_float)) if t is not None else None
     with torch.cuda.device(q.device):
-        rc = _lib.lib().fv_sdpa_segments_bf16(_stream_ptr(), vp(q), vp(k_all), vp(v_all), vp(out),
-                                              int(out.dtype == torch.bfloat16), bh, sq, nseg, _i32(seg_len),
-                                              _i32(seg_start), seg_rows, ctypes.c_float(scale), mode, bt, win, sink,
-                                              q_row0, fp(lse_out), fp(prev_o), fp(prev_lse))
+        rc = _lib.lib().fv_sdpa_segments_runs_bf16(_stream_ptr(), vp(q), vp(k_all), vp(v_all), vp(out),
+                                                   int(out.dtype == torch.bfloat16), bh, sq, nseg, _i32(seg_len),
+                                                   _i32(seg_start), seg_rows, ctypes.c_float(scale), mode, bt, win, sink,
+                                                   q_row0, q_split, q_row1, fp(lse_out), fp(prev_o), fp(prev_lse))
     _lib.check(rc, "segments_fwd")
     return out
 
 
 class SpLayout:
-    """Host-side bookkeeping of the exchange, pure Python: who holds which tokens, how the gathered
-    buffer is laid out ([world, bh, seg_rows, 128], shorter shards zero-padded to seg_rows), and the
-    segment tables of the two passes."""
+    """Host-side bookkeeping of the exchange, pure Python: which runs of the sequence each rank holds, how the
+    staging and gathered buffers are laid out, and the segment tables of the passes.
 
-    def __init__(self, seq: int, world: int, rank: int):
+    contiguous (the reference's split, rt/sp.rs:16-28): rank r holds ONE run, shard_ranges(seq, world)[r].
+    zigzag: the sequence is cut into 2 * world pieces and rank r holds piece r and piece 2 * world - 1 - r, an
+    early and a late one.  Under a causal mask a row sees about as many keys as its index, so contiguous shards
+    give the last rank several times the first rank's work; a zig-zag pair always adds up to about the same.
+
+    Every run lives in a slot of `run_rows` rows (the longest run of any rank; shorter ones are zero-padded), so
+    that one rank's K (or V) is a [runs, bh, run_rows, 128] block: `runs` key segments of the attention call."""
+
+    def __init__(self, seq: int, world: int, rank: int, zigzag: bool = False):
         if not 0 <= rank < max(world, 1):
             raise ValueError(f"SP rank {rank} out of world {world}")
-        self.seq, self.world, self.rank = seq, max(world, 1), rank
-        self.ranges = shard_ranges(seq, self.world)
-        self.start, self.len = self.ranges[rank]
-        self.seg_rows = max(l for _, l in self.ranges)
+        self.seq, self.world, self.rank, self.zigzag = seq, max(world, 1), rank, bool(zigzag) and world > 1
+        if self.zigzag:
+            pieces = shard_ranges(seq, 2 * self.world)
+            self.runs = [[pieces[r], pieces[2 * self.world - 1 - r]] for r in range(self.world)]
+        else:
+            self.runs = [[rg] for rg in shard_ranges(seq, self.world)]
+        self.nrun = len(self.runs[0])
+        self.ranges = [rr[0] for rr in self.runs]           # first run of every rank (the contiguous shard)
+        self.start, _ = self.runs[rank][0]
+        self.len = sum(l for _, l in self.runs[rank])      # rows this rank holds
+        self.run_rows = max(max(l for _, l in rr) for rr in self.runs)
+        self.seg_rows = self.run_rows
 
+    # ---- this rank's query rows
+    def q_runs(self):
+        """(q_row0, q_split, q_row1) of this rank's rows for the attention call."""
+        rr = self.runs[self.rank]
+        if len(rr) == 1 or rr[1][1] == 0:
+            return rr[0][0], 0, 0
+        if rr[0][1] == 0:
+            return rr[1][0], 0, 0
+        return rr[0][0], rr[0][1], rr[1][0]
+
+    def rows(self, rank: Optional[int] = None):
+        """Global row indices this rank (or `rank`) holds, in its local order."""
+        rr = self.runs[self.rank if rank is None else rank]
+        return [i for s, l in rr for i in range(s, s + l)]
+
+    # ---- key segments
     def pass1(self):
-        """(seg_len, seg_start) of the local-keys pass: one segment, this rank's shard."""
-        return [self.len], [self.start]
+        """(seg_len, seg_start) of the local-keys pass: this rank's own runs."""
+        rr = self.runs[self.rank]
+        return [l for _, l in rr], [s for s, _ in rr]
 
-    def pass2(self):
-        """(seg_len, seg_start) of the remote-keys pass over the gathered buffer: every rank's segment at
-        its global offset, this rank's own one emptied (pass 1 covered it)."""
-        lens = [l if r != self.rank else 0 for r, (_, l) in enumerate(self.ranges)]
-        return lens, [s for s, _ in self.ranges]
-
-    def needs_padding(self) -> bool:
-        return self.len != self.seg_rows
+    def needed(self, causal: Optional[BlockCausal]):
+        """{source rank: [run is needed]} over the other ranks: the runs that hold a key some row of this rank may
+        see.  Dense: every non-empty run.  Under the block-causal mask (rt/attn.rs:448-453) rows [a, b) see the
+        keys [lo, hi) and [0, sink * block): hi = the end of row b-1's block (it may reach past the run), lo = the
+        start of the oldest block inside row a's window (0 without a window)."""
+        mine = [(s, l) for s, l in self.runs[self.rank] if l > 0]
+        out = {}
+        for r in range(self.world):
+            if r == self.rank or not mine:
+                continue
+            flags = []
+            for s0, l in self.runs[r]:
+                need = l > 0
+                if need and causal is not None:
+                    bt = max(causal.block_tokens, 1)
+                    sink_hi = min(self.seq, causal.sink * bt)
+                    need = s0 < sink_hi
+                    for a, n in mine:
+                        hi = min(self.seq, ((a + n - 1) // bt + 1) * bt)
+                        lo = max(0, a // bt - causal.window + 1) * bt if causal.window > 0 else 0
+                        need = need or (s0 < hi and s0 + l > lo)
+                flags.append(need)
+            if any(flags):
+                out[r] = flags
+        return out
 
     def needed_ranks(self, causal: Optional[BlockCausal]) -> List[int]:
-        """The other ranks whose shard holds a key some row of this shard may see.  Dense: all of them.  Under
-        the block-causal mask (rt/attn.rs:448-453) the rows [start, start + len) see the keys
-        [lo, hi) and [0, sink * block): hi = the end of the last row's block (it may reach into the next shard),
-        lo = the start of the oldest block inside the first row's window (0 without a window)."""
-        others = [r for r in range(self.world) if r != self.rank]
-        if causal is None or self.len == 0:
-            return others if self.len else []
-        bt = max(causal.block_tokens, 1)
-        first, last = self.start, self.start + self.len - 1
-        hi = min(self.seq, (last // bt + 1) * bt)
-        lo = max(0, first // bt - causal.window + 1) * bt if causal.window > 0 else 0
-        sink_hi = min(self.seq, causal.sink * bt)
-        need = []
-        for r in others:
-            s0, l = self.ranges[r]
-            if l > 0 and ((s0 < hi and s0 + l > lo) or s0 < sink_hi):
-                need.append(r)
-        return need
+        return sorted(self.needed(causal))
+
+    def source_order(self, causal: Optional[BlockCausal]) -> List[int]:
+        """The needed source ranks, nearest first (rank - 1, rank - 2, ...): every rank then pulls from a different
+        peer at any one time."""
+        need = self.needed(causal)
+        return [r for r in ((self.rank - step) % self.world for step in range(1, self.world)) if r in need]
+
+    def source_segments(self, src: int, causal: Optional[BlockCausal]):
+        """(seg_len, seg_start) of one source rank's block, runs nobody here can see emptied."""
+        flags = self.needed(causal).get(src, [False] * self.nrun)
+        return [l if f else 0 for (_, l), f in zip(self.runs[src], flags)], [s for s, _ in self.runs[src]]
+
+    def pass2(self):
+        """(seg_len, seg_start) of ONE remote-keys pass over the whole gathered buffer [world, runs, ...]: every
+        run at its global offset, this rank's own ones emptied (pass 1 covered them)."""
+        return self.pass2_for(None)
 
     def pass2_for(self, causal: Optional[BlockCausal]):
-        """pass2() with the segments of ranks no row can see emptied: their shards are not fetched."""
-        need = set(self.needed_ranks(causal))
-        lens = [l if r in need else 0 for r, (_, l) in enumerate(self.ranges)]
-        return lens, [s for s, _ in self.ranges]
+        need = self.needed(causal)
+        lens, starts = [], []
+        for r in range(self.world):
+            flags = need.get(r, [False] * self.nrun)
+            for (s0, l), f in zip(self.runs[r], flags):
+                lens.append(l if (f and r != self.rank) else 0)
+                starts.append(s0)
+        return lens, starts
+
+    def needs_padding(self) -> bool:
+        return any(l != self.run_rows for _, l in self.runs[self.rank])
 
 
 class SpAttention:
-    """Sequence-parallel dense attention for one (seq, bh) shape; buffers allocated once.
+    """Sequence-parallel attention for one (seq, bh) shape; buffers allocated once.
 
-    groups: the heads are cut into that many contiguous groups, each with its own pair of all-gathers; the remote pass
-    of group g starts when group g has arrived, so only the first group's exchange has to hide under the local pass
-    (at 8 GPUs the whole exchange is longer than the local pass).  Default: 2 groups from 8 ranks on, else 1."""
+    Per call: this rank's K and V go into a staging block; the exchange brings every other rank's block into
+    this rank's own HBM on a communication stream while pass 1 (local keys) runs; then one pass per source rank,
+    nearest first, each as soon as that rank's block has landed, each continuing the previous pass' softmax
+    state (f32 result + log-sum-exp).  Only the first block's transfer has to hide under pass 1; every later one
+    hides under the pass before it.
 
-    def __init__(self, seq: int, bh: int, group=None, device=None, groups: Optional[int] = None):
-        import os
+    exchange="ce" (default): the staging block is peer-mapped (torch symmetric memory, multicast off) and the
+      other ranks PULL it with plain device-to-device copies that the copy engines carry out over NVLink -- no SM
+      is used, which matters because the attention kernel holds every SM for the whole launch.  The staging
+      block is double-buffered, so one device-side barrier per call is enough (when a rank passes the barrier of
+      call n + 1 every peer has finished pulling call n, and call n + 2 is the next one to write that half).
+    exchange="nccl": ncclAllGather of K and of V, then one remote pass over all of it."""
+
+    def __init__(self, seq: int, bh: int, group=None, device=None, zigzag: bool = False, exchange: Optional[str] = None):
         import torch.distributed as dist
-        self.dist = dist
-        self.group = group
+        self.dist, self.group = dist, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.seq, self.bh = seq, bh
-        self.layout = SpLayout(seq, self.world, self.rank)
-        self.ranges, self.start, self.len, self.seg_rows = (self.layout.ranges, self.layout.start, self.layout.len,
-                                                            self.layout.seg_rows)
+        self.layout = L = SpLayout(seq, self.world, self.rank, zigzag)
+        self.ranges, self.start, self.len, self.seg_rows = L.ranges, L.start, L.len, L.run_rows
+        self.calls = 0
         d = 128
-        if groups is None:
-            groups = int(os.environ.get("FV_SP_GROUPS", "0")) or (2 if self.world >= 8 else 1)
-        if groups < 1 or bh % groups != 0:
-            groups = 1
-        self.groups, self.bh_g = groups, bh // groups
-        if self.world > 1:
-            mk = lambda: torch.zeros((self.world, self.bh_g, self.seg_rows, d), dtype=torch.bfloat16, device=self.device)
-            self.k_all = [mk() for _ in range(groups)]
-            self.v_all = [mk() for _ in range(groups)]
-            self.o1 = torch.empty((bh, self.len, d), dtype=torch.float32, device=self.device)
-            self.lse1 = torch.empty((bh, self.len), dtype=torch.float32, device=self.device)
-            # The exchange runs on a HIGH-priority stream: the attention kernel keeps every SM busy with one large CTA each,
-            # and NCCL's copy CTAs only make progress once all of them are resident -- at default priority they trickle in
-            # as attention CTAs retire and the gather takes longer than the compute it should hide under (measured at 8
-            # GPUs: 14.3 ms per step against 9.9 ms without the exchange).
-            prio = int(os.environ.get("FV_SP_COMM_PRIORITY", "-1"))
-            self.comm_stream = torch.cuda.Stream(device=self.device, priority=prio)
-            # extra streams so that pulls from different peers run on different copy engines at the same time
-            ncopy = max(1, min(int(os.environ.get("FV_SP_COPY_STREAMS", "1")), self.world - 1))
-            self.copy_streams = [self.comm_stream] + [torch.cuda.Stream(device=self.device, priority=prio) for _ in range(ncopy - 1)]
-            self.pad = None
-            if self.layout.needs_padding():
-                self.pad = (torch.zeros((bh, self.seg_rows, d), dtype=torch.bfloat16, device=self.device),
-                            torch.zeros((bh, self.seg_rows, d), dtype=torch.bfloat16, device=self.device))
-            # How the shards travel.  "nccl": ncclAllGather (its copy CTAs compete with the attention CTAs for SMs).
-            # "ce": every rank keeps its K/V shard in a peer-mapped staging buffer and PULLS the other ranks' shards with
-            # plain device-to-device copies, which the copy engines carry out over NVLink without using any SM; two
-            # device-side barriers per call fence the staging buffer (written / everybody has pulled).
-            self.exchange = os.environ.get("FV_SP_EXCHANGE", "ce")
-            self.stage = self.hdl = self.released = None
-            if self.exchange == "ce":
-                try:
-                    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-                    import torch.distributed._symmetric_memory as symm_mem
-                    self.stage = symm_mem.empty((2, bh, self.seg_rows, d), dtype=torch.bfloat16, device=self.device)
-                    self.stage.zero_()
-                    self.hdl = symm_mem.rendezvous(self.stage, group if group is not None else dist.group.WORLD)
-                    self.peer = [self.hdl.get_buffer(r, (2, bh, self.seg_rows, d), torch.bfloat16) for r in range(self.world)]
-                except Exception as e:  # no peer mapping on this machine: say so and use NCCL
-                    import sys
-                    print(f"sp: peer-mapped staging unavailable ({type(e).__name__}: {e}); using the NCCL all-gather", file=sys.stderr)
-                    self.exchange, self.stage, self.hdl = "nccl", None, None
+        if self.world == 1:
+            return
+        blk = (L.nrun, bh, L.run_rows, d)
+        self.k_all = torch.zeros((self.world,) + blk, dtype=torch.bfloat16, device=self.device)
+        self.v_all = torch.zeros((self.world,) + blk, dtype=torch.bfloat16, device=self.device)
+        self.o_buf = [torch.empty((bh, self.len, d), dtype=torch.float32, device=self.device) for _ in range(2)]
+        self.lse_buf = [torch.empty((bh, self.len), dtype=torch.float32, device=self.device) for _ in range(2)]
+        prio = int(os.environ.get("FV_SP_COMM_PRIORITY", "-1"))
+        self.comm_stream = torch.cuda.Stream(device=self.device, priority=prio)
+        self.exchange = exchange or os.environ.get("FV_SP_EXCHANGE", "ce")
+        self.stage = self.hdl = None
+        self.fenced = [None, None]  # per staging half: the event after which it may be rewritten
+        if self.exchange == "ce":
+            try:
+                os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+                import torch.distributed._symmetric_memory as symm_mem
+                shape = (2, 2) + blk  # [half][k | v][run][bh][rows][d]
+                self.stage = symm_mem.empty(shape, dtype=torch.bfloat16, device=self.device)
+                self.stage.zero_()
+                self.hdl = symm_mem.rendezvous(self.stage, group if group is not None else dist.group.WORLD)
+                self.peer = [self.hdl.get_buffer(r, shape, torch.bfloat16) for r in range(self.world)]
+            except Exception as e:  # no peer mapping on this machine: say so and use NCCL
+                import sys
+                print(f"sp: peer-mapped staging unavailable ({type(e).__name__}: {e}); using the NCCL all-gather", file=sys.stderr)
+                self.exchange, self.stage, self.hdl = "nccl", None, None
+        if self.exchange != "ce":
+            self.local = torch.zeros((2,) + blk, dtype=torch.bfloat16, device=self.device)  # [k | v] padded block
+
+    def _fill(self, dst: torch.Tensor, x: torch.Tensor) -> None:
+        """This rank's [bh, len, d] rows into a [runs, bh, run_rows, d] block (padding rows stay zero)."""
+        off = 0
+        for r, (_, l) in enumerate(self.layout.runs[self.rank]):
+            if l:
+                dst[r, :, :l].copy_(x[:, off:off + l])
+            off += l
 
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None,
                 out: Optional[torch.Tensor] = None, causal: Optional[BlockCausal] = None) -> torch.Tensor:
-        """q, k, v: this rank's [bh, len_r, 128] bf16 shards.  Returns this rank's [bh, len_r, 128] bf16.
-        causal: the block-causal mask over GLOBAL token indices; a rank then fetches only the shards its rows
-        can see (later ranks do more work than earlier ones: contiguous shards are kept, as the reference's)."""
-        d = q.shape[-1]
+        """q, k, v: this rank's [bh, len_r, 128] bf16 rows (zig-zag: the early run followed by the late one).
+        Returns this rank's [bh, len_r, 128] bf16.  causal: the block-causal mask over GLOBAL token indices; a rank
+        then fetches only the runs its rows can see."""
+        L, d = self.layout, q.shape[-1]
         scale = float(scale) if scale is not None else 1.0 / d ** 0.5
+        q_row0, q_split, q_row1 = L.q_runs()
         if self.world == 1:
             return segments_fwd(q, k, v, [self.len], [0], self.len, scale, out=out, causal=causal)
-        need = self.layout.needed_ranks(causal)
         cur = torch.cuda.current_stream(self.device)
         if out is None:
             out = torch.empty((self.bh, self.len, d), dtype=torch.bfloat16, device=q.device)
-        G, n = self.groups, self.bh_g
-        no_comm = os.environ.get("FV_SP_NO_COMM") == "1"  # diagnosis only: compute without the exchange (wrong results)
-        arrived = []
+        order = L.source_order(causal)
+        half = self.calls & 1
+        self.calls += 1
+        arrived = {}
         if self.exchange == "ce":
-            if self.released is not None:
-                cur.wait_event(self.released)  # every rank has pulled the previous call's shard out of the staging buffer
-            self.stage[0, :, : self.len].copy_(k)
-            self.stage[1, :, : self.len].copy_(v)
-            ks, vs = self.stage[0], self.stage[1]
+            if self.fenced[half] is not None:
+                cur.wait_event(self.fenced[half])  # every rank has pulled what this half held two calls ago
+            mine_k, mine_v = self.stage[half, 0], self.stage[half, 1]
+            self._fill(mine_k, k)
+            self._fill(mine_v, v)
             ready = torch.cuda.Event()
             ready.record(cur)
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_event(ready)
-                if not no_comm:
-                    self.hdl.barrier(channel=0)  # every rank's staging buffer is written
+                self.hdl.barrier(channel=0)  # every rank's staging half is written (and its previous pulls are done)
                 fence = torch.cuda.Event()
                 fence.record(self.comm_stream)
-                for cs in self.copy_streams[1:]:
-                    cs.wait_event(fence)
-                for g in range(G):
-                    for step in range(1, self.world):
-                        r = (self.rank - step) % self.world
-                        if not no_comm and r in need:
-                            with torch.cuda.stream(self.copy_streams[(step - 1) % len(self.copy_streams)]):
-                                self.k_all[g][r].copy_(self.peer[r][0, g * n:(g + 1) * n], non_blocking=True)
-                                self.v_all[g][r].copy_(self.peer[r][1, g * n:(g + 1) * n], non_blocking=True)
-                    for cs in self.copy_streams[1:]:  # group g has arrived when every copy stream got this far
-                        e2 = torch.cuda.Event()
-                        e2.record(cs)
-                        self.comm_stream.wait_event(e2)
+                self.fenced[1 - half] = fence   # the OTHER half was last read one call ago: free from here on
+                for src in order:
+                    flags = L.needed(causal)[src]
+                    for r, f in enumerate(flags):
+                        if f:  # contiguous blocks: the copy engines move them, no kernel touches peer memory
+                            self.k_all[src, r].copy_(self.peer[src][half, 0, r], non_blocking=True)
+                            self.v_all[src, r].copy_(self.peer[src][half, 1, r], non_blocking=True)
                     ev = torch.cuda.Event()
                     ev.record(self.comm_stream)
-                    arrived.append(ev)
-                if not no_comm:
-                    self.hdl.barrier(channel=1)  # every rank has pulled: the staging buffers may be rewritten
-                self.released = torch.cuda.Event()
-                self.released.record(self.comm_stream)
+                    arrived[src] = ev
         else:
-            if self.pad is not None:
-                self.pad[0][:, : self.len].copy_(k)
-                self.pad[1][:, : self.len].copy_(v)
-                ks, vs = self.pad
-            else:
-                ks, vs = k, v
+            mine_k, mine_v = self.local[0], self.local[1]
+            self._fill(mine_k, k)
+            self._fill(mine_v, v)
             ready = torch.cuda.Event()
             ready.record(cur)
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_event(ready)
-                for g in range(G):
-                    if not no_comm:
-                        self.dist.all_gather_into_tensor(self.k_all[g].view(-1, self.seg_rows, d), ks[g * n:(g + 1) * n], group=self.group)
-                        self.dist.all_gather_into_tensor(self.v_all[g].view(-1, self.seg_rows, d), vs[g * n:(g + 1) * n], group=self.group)
-                    ev = torch.cuda.Event()
-                    ev.record(self.comm_stream)
-                    arrived.append(ev)
-        # pass 1: the local keys, every head, while the exchange is in flight
-        l1, s1 = self.layout.pass1()
-        l2, s2 = self.layout.pass2_for(causal)
-        if not any(l2):  # no row of this shard sees a key of another shard: pass 1 is the result
-            segments_fwd(q, ks, vs, l1, s1, self.seg_rows, scale, out=out, causal=causal, q_row0=self.start)
+                self.dist.all_gather_into_tensor(self.k_all, mine_k, group=self.group)
+                self.dist.all_gather_into_tensor(self.v_all, mine_v, group=self.group)
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+                arrived = {src: ev for src in order}
+        # pass 1: the local keys, while the exchange is in flight
+        l1, s1 = L.pass1()
+        common = dict(causal=causal, q_row0=q_row0, q_split=q_split, q_row1=q_row1)
+        if not order:  # no row of this rank sees a key of another rank: pass 1 is the result
+            segments_fwd(q, mine_k, mine_v, l1, s1, L.run_rows, scale, out=out, **common)
+            for ev in set(arrived.values()):
+                cur.wait_event(ev)  # (nccl: the gather still reads this rank's block)
             return out
-        segments_fwd(q, ks, vs, l1, s1, self.seg_rows, scale, out=self.o1, lse_out=self.lse1, causal=causal,
-                     q_row0=self.start)
-        # pass 2 per head group, as it arrives: every other rank's keys, merged with pass 1
-        for g in range(G):
-            cur.wait_event(arrived[g])
-            sl = slice(g * n, (g + 1) * n)
-            segments_fwd(q[sl], self.k_all[g], self.v_all[g], l2, s2, self.seg_rows, scale, out=out[sl],
-                         prev_o=self.o1[sl], prev_lse=self.lse1[sl], causal=causal, q_row0=self.start)
+        segments_fwd(q, mine_k, mine_v, l1, s1, L.run_rows, scale, out=self.o_buf[0], lse_out=self.lse_buf[0], **common)
+        if self.exchange == "ce":
+            # one pass per source rank as its block lands, each continuing the state of the one before
+            for n, src in enumerate(order):
+                cur.wait_event(arrived[src])
+                ln, st = L.source_segments(src, causal)
+                last = n == len(order) - 1
+                a, b = n & 1, 1 - (n & 1)
+                segments_fwd(q, self.k_all[src], self.v_all[src], ln, st, L.run_rows, scale,
+                             out=out if last else self.o_buf[b], lse_out=None if last else self.lse_buf[b],
+                             prev_o=self.o_buf[a], prev_lse=self.lse_buf[a], **common)
+        else:
+            cur.wait_event(arrived[order[0]])
+            ln, st = L.pass2_for(causal)
+            segments_fwd(q, self.k_all.view(-1, self.bh, L.run_rows, d), self.v_all.view(-1, self.bh, L.run_rows, d), ln, st,
+                         L.run_rows, scale, out=out, prev_o=self.o_buf[0], prev_lse=self.lse_buf[0], **common)
         return out
 
 

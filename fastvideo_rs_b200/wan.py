@@ -81,3 +81,60 @@ class WanSelfAttention:
         q, k, v = qk_prep(qkv, self.wq, self.wk, self.cos, self.sin, self.heads, eps=self.eps)
         plan = Plan.block_causal(scale, self.causal) if self.causal is not None else Plan.dense(scale)
         return sdpa(q, k, v, plan)
+
+
+class HostStaged:
+    """Runs a device step over a sequence of HOST batches with the copies off the critical path: inputs come
+    from pinned host tensors, results go back to pinned host tensors, and while step i computes, the input of
+    step i + 1 is already arriving and the result of step i - 1 is leaving -- two device buffers each way, one
+    stream for host-to-device copies, one for device-to-host copies, events in between.  This is what the
+    denoising loop does around attention when its activations live on the host (offload), and what the
+    benchmark's end-to-end leg measures.
+
+    step(dev_in) -> dev_out runs on the current stream and may return a view of a buffer it reuses: the result
+    is copied into this object's own output buffer on the compute stream before the next step starts."""
+
+    def __init__(self, in_shape, out_shape, device, dtype=torch.bfloat16):
+        self.device = device
+        self.h2d, self.d2h = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+        self.dev_in = [torch.empty(in_shape, dtype=dtype, device=device) for _ in range(2)]
+        self.dev_out = [torch.empty(out_shape, dtype=dtype, device=device) for _ in range(2)]
+
+    def run(self, host_ins, host_outs, step):
+        """host_ins / host_outs: equally long lists of pinned host tensors (entries may repeat)."""
+        cur = torch.cuda.current_stream(self.device)
+        n = len(host_ins)
+        arrived = [None, None]   # input buffer i % 2 holds batch i
+        consumed = [None, None]  # ... and the step that read it has finished
+        left = [None, None]      # output buffer i % 2 has been copied out
+
+        def fetch(i):
+            with torch.cuda.stream(self.h2d):
+                if consumed[i & 1] is not None:
+                    self.h2d.wait_event(consumed[i & 1])
+                self.dev_in[i & 1].copy_(host_ins[i], non_blocking=True)
+                arrived[i & 1] = torch.cuda.Event()
+                arrived[i & 1].record(self.h2d)
+
+        if n:
+            fetch(0)
+        for i in range(n):
+            if i + 1 < n:
+                fetch(i + 1)
+            cur.wait_event(arrived[i & 1])
+            out = step(self.dev_in[i & 1])
+            consumed[i & 1] = torch.cuda.Event()
+            consumed[i & 1].record(cur)
+            if left[i & 1] is not None:
+                cur.wait_event(left[i & 1])
+            self.dev_out[i & 1].view(-1)[: out.numel()].copy_(out.reshape(-1))
+            done = torch.cuda.Event()
+            done.record(cur)
+            with torch.cuda.stream(self.d2h):
+                self.d2h.wait_event(done)
+                host_outs[i].view(-1)[: out.numel()].copy_(self.dev_out[i & 1].view(-1)[: out.numel()], non_blocking=True)
+                left[i & 1] = torch.cuda.Event()
+                left[i & 1].record(self.d2h)
+        for ev in left:
+            if ev is not None:
+                cur.wait_event(ev)

@@ -233,6 +233,68 @@ def test_sequence_parallel_block_causal_rank_by_rank(fvlib, oracle, world, bt, w
     assert_close(to_host_f32(got), oracle.sdpa_rows(q, k, v, block_causal=(bt, win, sink)), f"sp{world} causal bt{bt} w{win} s{sink}")
 
 
+@pytest.mark.parametrize("world,zigzag,mask", [(2, False, None), (4, False, None), (4, True, (130, 0, 0)), (3, True, (64, 2, 1)),
+                                               (8, True, (100, 0, 0)), (4, True, None)])
+def test_sequence_parallel_chained_passes_rank_by_rank(fvlib, oracle, world, zigzag, mask):
+    """The launches of SpAttention.forward with the copy-engine exchange, run rank after rank on one GPU: pass 1
+    over the rank's own runs, then one pass per source rank in SpLayout.source_order, each continuing the
+    previous pass' f32 state -- contiguous shards and the zig-zag split (two runs of query rows per rank), dense
+    and block-causal.  Runs a rank does not fetch are poisoned with NaN.  Put back in sequence order the rows
+    equal the one-launch kernel and the oracle."""
+    from fastvideo_rs_b200 import sdpa, sp
+    bh, seq = 2, 1001
+    q, k, v = qkv(oracle, 91 + world, bh, seq, seq)
+    tq, tk, tv = to_dev_bf16(q), to_dev_bf16(k), to_dev_bf16(v)
+    causal = sdpa.BlockCausal(*mask) if mask else None
+    scale = 1.0 / math.sqrt(128)
+    layouts = [sp.SpLayout(seq, world, r, zigzag=zigzag) for r in range(world)]
+    L0 = layouts[0]
+
+    def block(t, lay):  # a rank's [runs, bh, run_rows, 128] block
+        b = torch.zeros((lay.nrun, bh, lay.run_rows, 128), dtype=torch.bfloat16, device="cuda")
+        for r, (s0, l) in enumerate(lay.runs[lay.rank]):
+            b[r, :, :l] = t[:, s0:s0 + l]
+        return b
+
+    kb = [block(tk, lay) for lay in layouts]
+    vb = [block(tv, lay) for lay in layouts]
+    got = torch.zeros((bh, seq, 128), dtype=torch.bfloat16, device="cuda")
+    for lay in layouts:
+        rows = torch.tensor(lay.rows(), device="cuda", dtype=torch.long)
+        if rows.numel() == 0:
+            continue
+        qr = tq[:, rows].contiguous()
+        q_row0, q_split, q_row1 = lay.q_runs()
+        common = dict(causal=causal, q_row0=q_row0, q_split=q_split, q_row1=q_row1)
+        l1, s1 = lay.pass1()
+        order = lay.source_order(causal)
+        if not order:
+            o = sp.segments_fwd(qr, kb[lay.rank], vb[lay.rank], l1, s1, lay.run_rows, scale, **common)
+        else:
+            ob = [torch.empty((bh, lay.len, 128), dtype=torch.float32, device="cuda") for _ in range(2)]
+            lb = [torch.empty((bh, lay.len), dtype=torch.float32, device="cuda") for _ in range(2)]
+            sp.segments_fwd(qr, kb[lay.rank], vb[lay.rank], l1, s1, lay.run_rows, scale, out=ob[0], lse_out=lb[0], **common)
+            o = None
+            for n, src in enumerate(order):
+                ln, st = lay.source_segments(src, causal)
+                ks, vs = kb[src].clone(), vb[src].clone()
+                for run, l in enumerate(ln):
+                    if l == 0:  # not fetched
+                        ks[run].fill_(float("nan"))
+                        vs[run].fill_(float("nan"))
+                last = n == len(order) - 1
+                a, b = n & 1, 1 - (n & 1)
+                o = sp.segments_fwd(qr, ks, vs, ln, st, lay.run_rows, scale, out=None if last else ob[b],
+                                    lse_out=None if last else lb[b], prev_o=ob[a], prev_lse=lb[a], **common)
+        got[:, rows] = o
+    assert sdpa.device_status() == 0
+    assert torch.isfinite(got.float()).all()
+    one = sdpa.dense_fwd(tq, tk, tv, causal=causal)
+    assert float((got.float() - one.float()).abs().max()) <= 2e-2
+    assert_close(to_host_f32(got), oracle.sdpa_rows(q, k, v, block_causal=mask), f"sp{world} zigzag={zigzag} mask={mask}")
+    assert L0.nrun == (2 if zigzag else 1)
+
+
 def test_merged_heads_output_is_the_permuted_bhsd_output(fvlib, oracle):
     """merge_heads folded into the store (rt/ops.rs:2373-2385): same bits as the BHSD call, [b, s, h*d] order."""
     from fastvideo_rs_b200 import sdpa

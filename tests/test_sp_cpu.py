@@ -142,7 +142,7 @@ def test_needed_ranks_under_the_block_causal_mask():
                 assert [i for i, l in enumerate(lens) if l] == sorted(need)
                 assert starts == [s for s, _ in lay.ranges]
         lay = sp.SpLayout(seq, world, 0)
-        assert lay.needed_ranks(None) == [r for r in range(1, world)] or lay.len == 0
+        assert lay.needed_ranks(None) == [r for r in range(1, world) if lay.ranges[r][1] > 0] or lay.len == 0
 
 
 def test_native_sp_handle_argument_checks_without_a_gpu():
@@ -153,7 +153,7 @@ def test_native_sp_handle_argument_checks_without_a_gpu():
     from fastvideo_rs_b200 import _lib
     L = _lib.lib()
     h = ctypes.c_void_p()
-    for world, rank, seq, bh in ((2, 2, 100, 4), (0, 0, 100, 4), (9, 0, 100, 4), (1, 0, 0, 4), (1, 0, 100, 0), (2, -1, 100, 4)):
+    for world, rank, seq, bh in ((2, 2, 100, 4), (0, 0, 100, 4), (17, 0, 100, 4), (1, 0, 0, 4), (1, 0, 100, 0), (2, -1, 100, 4)):
         assert L.fv_sp_create(None, world, rank, seq, bh, 0, ctypes.byref(h)) == _lib.ERR_INVALID, (world, rank, seq, bh)
         assert not h.value
     assert L.fv_sp_create(None, 2, 0, 100, 4, 0, ctypes.byref(h)) == _lib.ERR_INVALID  # two ranks need an id
@@ -179,7 +179,7 @@ def test_dense_second_pass_table_is_unchanged_by_the_mask_plumbing():
             lay = sp.SpLayout(seq, world, rank)
             if lay.len:
                 assert lay.pass2_for(None) == lay.pass2()
-                assert lay.needed_ranks(None) == [r for r in range(world) if r != rank]
+                assert lay.needed_ranks(None) == [r for r in range(world) if r != rank and lay.ranges[r][1] > 0]
 
 
 def test_native_second_pass_table_equals_the_python_layout():
@@ -201,6 +201,44 @@ def test_native_second_pass_table_equals_the_python_layout():
                 if lay.len == 0 and bc is not None:
                     continue  # a rank without rows computes nothing: its table is not used
                 assert list(lens) == want, (seq, world, rank, bc, list(lens), want)
-    lens = (ctypes.c_int * 8)()
-    assert L.fv_sp_second_pass_lens(100, 9, 0, 0, 0, 0, 0, lens) == _lib.ERR_INVALID
+    lens = (ctypes.c_int * 32)()
+    assert L.fv_sp_second_pass_lens(100, 17, 0, 0, 0, 0, 0, lens) == _lib.ERR_INVALID
     assert L.fv_sp_second_pass_lens(100, 2, 2, 0, 0, 0, 0, lens) == _lib.ERR_INVALID
+
+
+def test_zigzag_layout_balances_the_causal_work_and_covers_the_sequence():
+    """Zig-zag split: rank r holds piece r and piece 2 * world - 1 - r of 2 * world pieces.  Every token is held
+    once; under the chunk-causal mask of the Self-Forcing shape the ranks' visible (row, key) pairs differ by
+    well under one per cent, where contiguous shards differ by a factor of several."""
+    from fastvideo_rs_b200 import sp
+    from fastvideo_rs_b200.sdpa import BlockCausal
+    seq, world, bc = 32760, 8, BlockCausal(4680)
+    work = lambda rows: sum(min(seq, (i // bc.block_tokens + 1) * bc.block_tokens) for i in rows)
+    held, zz, contiguous = [], [], []
+    for r in range(world):
+        lay = sp.SpLayout(seq, world, r, zigzag=True)
+        rows = lay.rows()
+        held += rows
+        zz.append(work(rows))
+        q0, split, q1 = lay.q_runs()
+        assert rows[0] == q0 and rows[split] == q1 and split == lay.runs[r][0][1]
+        contiguous.append(work(sp.SpLayout(seq, world, r).rows()))
+    assert sorted(held) == list(range(seq))
+    assert max(zz) / min(zz) < 1.005 and max(contiguous) / min(contiguous) > 3.0
+    # what a rank fetches under the mask, against the predicate itself (small case, every pair)
+    for seq, world in ((200, 4), (37, 3)):
+        for bc in (BlockCausal(25), BlockCausal(16, 2, 1), BlockCausal(7, 0, 2)):
+            for rank in range(world):
+                lay = sp.SpLayout(seq, world, rank, zigzag=True)
+                need = lay.needed(bc)
+                for src in range(world):
+                    if src == rank:
+                        continue
+                    for run, (s0, l) in enumerate(lay.runs[src]):
+                        truth = any(bc.allows(qi, ki) for qi in lay.rows() for ki in range(s0, s0 + l))
+                        got = need.get(src, [False] * lay.nrun)[run]
+                        assert got or not truth, (seq, world, bc, rank, src, run)
+                        if bc.window == 0:
+                            assert got == truth, (seq, world, bc, rank, src, run)
+                lens, starts = lay.pass2_for(bc)
+                assert len(lens) == world * lay.nrun and all(l == 0 for l in lens[rank * lay.nrun:(rank + 1) * lay.nrun])
