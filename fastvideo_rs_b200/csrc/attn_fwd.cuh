@@ -52,7 +52,8 @@
 //                   exponentials per tile is exactly as long as the tile's two MMAs: moving a share of them
 //                   to the FMA pipe, evenly interleaved, is what lets the two overlap.
 //   FV_ATT_SPLIT    TMEM map: 1 = S_A S_B O_A O_B, 0 = S_A O_A S_B O_B (no measurable difference)
-//   FV_ATT_BACKOFF  nanoseconds a waiting thread sleeps between two probes of its barrier (0 = none)
+//   FV_ATT_BACKOFF  nanoseconds a waiting softmax thread sleeps between two probes of its barrier (0 = none);
+//                   FV_ATT_BACKOFF_LOADER the same for the loader thread
 #ifndef FV_ATT_POLY
 #define FV_ATT_POLY 0
 #endif
@@ -61,6 +62,9 @@
 #endif
 #ifndef FV_ATT_BACKOFF
 #define FV_ATT_BACKOFF 0
+#endif
+#ifndef FV_ATT_BACKOFF_LOADER
+#define FV_ATT_BACKOFF_LOADER 0
 #endif
 
 #define FV_ST_BAD_SMEM 90  // dynamic shared memory is not 1024-byte aligned (the swizzled tiles need it)
@@ -310,9 +314,11 @@ struct Waiter {
         const long long t0 = clock64();
         uint32_t n = 0;
         while (!mbar_try(bar, parity)) {
-#if FV_ATT_BACKOFF > 0
-            __nanosleep(FV_ATT_BACKOFF);
-#endif
+            if (role == 1) {
+                if (FV_ATT_BACKOFF_LOADER > 0) __nanosleep(FV_ATT_BACKOFF_LOADER);
+            } else if (role == 3) {
+                if (FV_ATT_BACKOFF > 0) __nanosleep(FV_ATT_BACKOFF);
+            }
             if (((++n) & 63u) == 0u) {
                 uint32_t gone;
                 asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(gone) : "r"(sbase + Smem::abort_flag) : "memory");
