@@ -10,7 +10,15 @@
 #include "fv_runtime.h"
 #include <cuda_bf16.h>
 #include <dlfcn.h>
+#include <stdlib.h>
+#include <time.h>
 #include <mutex>
+#if __has_include(<nccl.h>)
+#include <nccl.h>  // types only (ncclConfig_t for the non-blocking rendezvous); every call goes through dlsym
+#define FV_HAVE_NCCL_H 1
+#else
+#define FV_HAVE_NCCL_H 0
+#endif
 #include <string.h>
 #include <vector>
 
@@ -32,6 +40,10 @@ struct Nccl {
     int (*CommDestroy)(void*) = nullptr;
     int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
+    // optional (NCCL >= 2.14): the non-blocking rendezvous
+    int (*CommInitRankConfig)(void**, int, NcclId, int, void*) = nullptr;
+    int (*CommGetAsyncError)(void*, int*) = nullptr;
+    int (*CommAbort)(void*) = nullptr;
 };
 static Nccl g_nccl;
 static std::mutex g_nccl_mu;
@@ -48,6 +60,9 @@ static int load_nccl() {
     n.CommDestroy = reinterpret_cast<decltype(n.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
     n.AllGather = reinterpret_cast<decltype(n.AllGather)>(dlsym(h, "ncclAllGather"));
     n.GetErrorString = reinterpret_cast<decltype(n.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+    n.CommInitRankConfig = reinterpret_cast<decltype(n.CommInitRankConfig)>(dlsym(h, "ncclCommInitRankConfig"));
+    n.CommGetAsyncError = reinterpret_cast<decltype(n.CommGetAsyncError)>(dlsym(h, "ncclCommGetAsyncError"));
+    n.CommAbort = reinterpret_cast<decltype(n.CommAbort)>(dlsym(h, "ncclCommAbort"));
     if (!n.GetUniqueId || !n.CommInitRank || !n.CommDestroy || !n.AllGather || !n.GetErrorString) {
         dlclose(h);
         return fvrt::fail(FV_ERR_NCCL, "libnccl.so.2 lacks a symbol this library needs");
@@ -165,6 +180,11 @@ static int forward(Sp* s, cudaStream_t stream, const void* q, const void* k, con
     visible_lens(s->seq, s->world, s->rank, s->starts.data(), s->lens.data(), mask_mode, bt, window, sink, lens2.data());
     bool any = false;
     for (int r = 0; r < s->world; r++) any = any || lens2[r] > 0;
+    // From here on the gathers are enqueued and read this rank's shard: whatever happens, the caller's stream
+    // must not run ahead of them.
+    auto wait_all = [&]() {
+        for (int g = 0; g < s->groups; g++) cudaStreamWaitEvent(stream, s->arrived[g], 0);
+    };
     const int len1 = s->len, start1 = s->start;
     if (!any) {  // no row of this shard sees a key of another shard: pass 1 is the result
         rc = fv_sdpa_segments_bf16(stream, q, ks, vs, out, out_is_bf16, s->bh, s->len, 1, &len1, &start1, s->seg_rows, scale,
@@ -173,7 +193,10 @@ static int forward(Sp* s, cudaStream_t stream, const void* q, const void* k, con
         rc = fv_sdpa_segments_bf16(stream, q, ks, vs, s->o1, 0, s->bh, s->len, 1, &len1, &start1, s->seg_rows, scale, mask_mode,
                                    bt, window, sink, s->start, s->lse1, nullptr, nullptr);
     }
-    if (rc != FV_RAN) return rc;
+    if (rc != FV_RAN) {
+        wait_all();
+        return rc;
+    }
     const size_t q_group = (size_t)s->bh_g * s->len * kD;
     for (int g = 0; g < s->groups; g++) {
         // Also when pass 2 is skipped: the gather reads this rank's shard, which the caller may rewrite after this call.
@@ -185,12 +208,57 @@ static int forward(Sp* s, cudaStream_t stream, const void* q, const void* k, con
                                    out_is_bf16, s->bh_g, s->len, s->world, lens2.data(), s->starts.data(), s->seg_rows, scale,
                                    mask_mode, bt, window, sink, s->start, nullptr, s->o1 + g * q_group,
                                    s->lse1 + (size_t)g * s->bh_g * s->len);
-        if (rc != FV_RAN) return rc;
+        if (rc != FV_RAN) {
+            wait_all();
+            return rc;
+        }
     }
     return FV_RAN;
 }
 
-static int create(const void* unique_id, int world, int rank, int seq, int bh, int groups, Sp** out) {
+// Rendezvous with a deadline.  ncclCommInitRank blocks for as long as a rank is missing; with NCCL's
+// non-blocking mode the communicator is polled instead and, when the deadline passes, aborted: the caller
+// gets FV_ERR_NCCL and a usable process back.  (Needs nccl.h at build time for ncclConfig_t and NCCL >= 2.14
+// at run time; otherwise the blocking call is all there is.)
+static int init_comm(Sp* s, const NcclId& id, int world, int rank, double timeout_s) {
+#if FV_HAVE_NCCL_H
+    if (timeout_s > 0 && g_nccl.CommInitRankConfig && g_nccl.CommGetAsyncError && g_nccl.CommAbort) {
+        ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+        cfg.blocking = 0;
+        int nrc = g_nccl.CommInitRankConfig(&s->comm, world, id, rank, &cfg);
+        if (nrc != 0 && nrc != (int)ncclInProgress)
+            return fvrt::fail(FV_ERR_NCCL, "ncclCommInitRankConfig: %s", g_nccl.GetErrorString(nrc));
+        timespec t0;
+        clock_gettime(CLOCK_MONOTONIC, &t0);
+        for (;;) {
+            int state = 0;
+            nrc = g_nccl.CommGetAsyncError(s->comm, &state);
+            if (nrc != 0) return fvrt::fail(FV_ERR_NCCL, "ncclCommGetAsyncError: %s", g_nccl.GetErrorString(nrc));
+            if (state == 0) return FV_RAN;
+            if (state != (int)ncclInProgress) {
+                g_nccl.CommAbort(s->comm);
+                s->comm = nullptr;
+                return fvrt::fail(FV_ERR_NCCL, "sp: communicator of %d ranks failed to form: %s", world, g_nccl.GetErrorString(state));
+            }
+            timespec t1;
+            clock_gettime(CLOCK_MONOTONIC, &t1);
+            if ((double)(t1.tv_sec - t0.tv_sec) + 1e-9 * (double)(t1.tv_nsec - t0.tv_nsec) > timeout_s) {
+                g_nccl.CommAbort(s->comm);
+                s->comm = nullptr;
+                return fvrt::fail(FV_ERR_NCCL, "sp: rank %d waited %.1f s for the other %d rank(s) of the communicator: rendezvous abandoned",
+                                  rank, timeout_s, world - 1);
+            }
+            const timespec nap = {0, 2000000};
+            nanosleep(&nap, nullptr);
+        }
+    }
+#endif
+    const int nrc = g_nccl.CommInitRank(&s->comm, world, id, rank);
+    if (nrc != 0) return fvrt::fail(FV_ERR_NCCL, "ncclCommInitRank: %s", g_nccl.GetErrorString(nrc));
+    return FV_RAN;
+}
+
+static int create(const void* unique_id, int world, int rank, int seq, int bh, int groups, double timeout_s, Sp** out) {
     if (!out) return fvrt::fail(FV_ERR_INVALID, "sp: null handle pointer");
     *out = nullptr;
     if (world < 1 || rank < 0 || rank >= world) return fvrt::fail(FV_ERR_INVALID, "sp: rank %d out of world %d", rank, world);
@@ -260,8 +328,29 @@ static int create(const void* unique_id, int world, int rank, int seq, int bh, i
 #undef FV_TRY
     NcclId id;
     memcpy(id.bytes, unique_id, sizeof(id.bytes));
-    const int nrc = g_nccl.CommInitRank(&s->comm, world, id, rank);
-    if (nrc != 0) return bail(fvrt::fail(FV_ERR_NCCL, "ncclCommInitRank: %s", g_nccl.GetErrorString(nrc)));
+    rc = init_comm(s, id, world, rank, timeout_s);
+    if (rc != FV_RAN) return bail(rc);
+    // Every rank must describe the same problem: a rank with another seq, bh or group count would size its
+    // gathers differently and the first exchange would never complete.  One small all-gather settles it here,
+    // where a mismatch is an error return on every rank instead of a hang later.
+    {
+        int* shape_dev = nullptr;
+        const int mine[4] = {seq, bh, groups, world};
+        std::vector<int> all(4 * (size_t)world);
+        cudaError_t e = cudaMalloc(&shape_dev, sizeof(int) * 4 * ((size_t)world + 1));
+        if (e == cudaSuccess) e = cudaMemcpy(shape_dev + 4 * (size_t)world, mine, sizeof(mine), cudaMemcpyHostToDevice);
+        int nrc = 0;
+        if (e == cudaSuccess) nrc = g_nccl.AllGather(shape_dev + 4 * (size_t)world, shape_dev, 16, /* ncclInt8 */ 0, s->comm, s->comm_stream);
+        if (e == cudaSuccess && nrc == 0) e = cudaStreamSynchronize(s->comm_stream);
+        if (e == cudaSuccess && nrc == 0) e = cudaMemcpy(all.data(), shape_dev, sizeof(int) * 4 * (size_t)world, cudaMemcpyDeviceToHost);
+        if (shape_dev) cudaFree(shape_dev);
+        if (nrc != 0) return bail(fvrt::fail(FV_ERR_NCCL, "sp: shape handshake: %s", g_nccl.GetErrorString(nrc)));
+        if (e != cudaSuccess) return bail(fvrt::fail(FV_ERR_CUDA, "sp: shape handshake: %s", cudaGetErrorString(e)));
+        for (int r = 0; r < world; r++)
+            if (memcmp(&all[4 * (size_t)r], mine, sizeof(mine)) != 0)
+                return bail(fvrt::fail(FV_ERR_INVALID, "sp: rank %d was created with seq %d, bh %d, groups %d, world %d; this rank (%d) with %d, %d, %d, %d",
+                                       r, all[4 * r], all[4 * r + 1], all[4 * r + 2], all[4 * r + 3], rank, seq, bh, groups, world));
+    }
     *out = s;
     return FV_RAN;
 }
@@ -290,13 +379,21 @@ extern "C" int fv_sp_second_pass_lens(int seq, int world, int rank, int mask_mod
     return FV_RAN;
 }
 
-extern "C" int fv_sp_create(const void* unique_id, int world, int rank, int seq, int bh, int groups, void** sp_out) {
+extern "C" int fv_sp_create_timeout(const void* unique_id, int world, int rank, int seq, int bh, int groups,
+                                    double timeout_seconds, void** sp_out) {
     fvrt::clear_error();
     fvsp::Sp* s = nullptr;
-    const int rc = fvsp::create(unique_id, world, rank, seq, bh, groups, &s);
+    const int rc = fvsp::create(unique_id, world, rank, seq, bh, groups, timeout_seconds, &s);
     if (sp_out) *sp_out = s;
     else if (s) fvsp::release(s);
     return rc;
+}
+
+extern "C" int fv_sp_create(const void* unique_id, int world, int rank, int seq, int bh, int groups, void** sp_out) {
+    // FV_SP_INIT_TIMEOUT_S: seconds to wait for the other ranks (default 120; 0 = NCCL's own blocking rendezvous)
+    const char* e = getenv("FV_SP_INIT_TIMEOUT_S");
+    const double t = e ? atof(e) : 120.0;
+    return fv_sp_create_timeout(unique_id, world, rank, seq, bh, groups, t, sp_out);
 }
 
 extern "C" int fv_sp_destroy(void* sp) {

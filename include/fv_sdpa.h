@@ -204,6 +204,27 @@ FV_API int fv_wan_rope_tables(int ppf, int pph, int ppw, int d, double theta, in
  * vsa_attention_device (:358-470) with its launchers (rt/ops.rs:811-923,1074-1383,1554-1619;
  * rt/attn_dc.rs:275-604); arithmetic of the host twin vsa_attention_host (rt/vsa.rs:116-262). */
 
+/* ---- the block glue either side of self-attention (bf16 activations) ---------------------------------
+ * e: the block's AdaLN table, f32 [batch, e_rows, dim] (6 rows in Wan: shift/scale/gate of attention and FFN);
+ * hidden rows are [batch * seq, dim] bf16, dim a multiple of 8, at most 6 144.  Both are one pass over HBM: a
+ * row is read once and kept in registers for both LayerNorm statistics.
+ *
+ * fv_wan_ln_adaln_bf16 replaces CudaTensor::ln_adaln_e under bf16 activations
+ *   (crates/fastvideo-cudarc/src/rt/fused.rs:20-70 -> rt/act16.rs:253-275, kernel rt/kernels/act16.cu:184-209;
+ *   the call before attention, wan/transformer.rs:949-953):
+ *   out = bf16( (x - mean) * rsqrt(var + eps) * (1 + e[b, scale_slot]) + e[b, shift_slot] ), f32 statistics.
+ * fv_wan_self_residual_norm_bf16 replaces wan::fuse::self_residual_norm (crates/fastvideo-cudarc/src/wan/fuse.rs:
+ *   108-166, kernel wan/kernels/block.cu:54-78 with res_mode 0 / ln_mode 0; the call after attention,
+ *   wan/transformer.rs:959-971): s = hidden + attn * e[b, gate_slot] in f32 (product and sum rounded separately);
+ *   hidden_out = bf16(s); normed_out = bf16( LN(s) * norm_w + norm_b ) with the statistics of the UNROUNDED s
+ *   (FastVideo's rounding points).  norm_w, norm_b f32 [dim].
+ * Declines: dim not a multiple of 8 or above 6 144, empty sizes. */
+FV_API int fv_wan_ln_adaln_bf16(void* stream, const void* x, const float* e, int scale_slot, int shift_slot, int batch,
+                                int seq, int dim, int e_rows, float eps, void* out);
+FV_API int fv_wan_self_residual_norm_bf16(void* stream, const void* hidden, const void* attn, const float* e, int gate_slot,
+                                          const float* norm_w, const float* norm_b, int batch, int seq, int dim, int e_rows,
+                                          float eps, void* hidden_out, void* normed_out);
+
 /* topk_for: clamp(ceil((1 - sparsity) * num_tiles), 1, num_tiles). */
 FV_API int fv_vsa_topk_for(double sparsity, int num_tiles);
 
@@ -382,7 +403,9 @@ FV_API void fv_shard_ranges(int seq, int world, int* start, int* len);
  * fv_sp_info: this rank's first token, its shard length, the longest shard, the head groups.
  * fv_sp_forward_bf16: q, k, v [bh, len, 128] bf16 shards of this rank, out [bh, len, 128] bf16 or f32.
  *   mask_mode FV_MASK_BLOCK_CAUSAL applies the mask of fv_sdpa_dense_bf16 over GLOBAL token indices; shards no
- *   row of this rank can see are left out of the second pass.  Asynchronous on `stream` (on return `stream`
+ *   row of this rank can see are left out of the second pass.  An error return from one rank alone (a null
+ *   operand, a handle used on another device) happens before that rank joins the exchange: the other ranks'
+ *   gathers then never complete, so treat it as fatal for the communicator (destroy the handles).  Asynchronous on `stream` (on return `stream`
  *   is ordered after the exchange, so k and v may be rewritten by later work on it); calls on one handle must
  *   be issued in the same order on every rank and from one stream at a time.  A rank without rows (more ranks
  *   than tokens) still calls: it takes part in the exchange and computes nothing (its operands may be null).
@@ -395,6 +418,14 @@ FV_API int fv_sp_second_pass_lens(int seq, int world, int rank, int mask_mode, i
                                   int* lens_out);
 FV_API int fv_sp_unique_id(void* id_out_128_bytes);
 FV_API int fv_sp_create(const void* unique_id, int world, int rank, int seq, int bh, int groups, void** sp_out);
+/* fv_sp_create with an explicit rendezvous deadline: a rank that waits longer than timeout_seconds for the
+ * others gives the communicator up (ncclCommAbort) and returns FV_ERR_NCCL instead of blocking for ever;
+ * timeout_seconds <= 0 uses NCCL's own blocking rendezvous.  fv_sp_create uses FV_SP_INIT_TIMEOUT_S (default
+ * 120).  After the rendezvous the ranks compare (seq, bh, groups, world): a rank created with other numbers
+ * makes every rank return FV_ERR_INVALID here, not hang in the first exchange.  The reference has no
+ * rendezvous at all (its ranks are threads of one process, crates/fastvideo-cudarc/src/rt/sdpa.rs:371-410). */
+FV_API int fv_sp_create_timeout(const void* unique_id, int world, int rank, int seq, int bh, int groups,
+                                double timeout_seconds, void** sp_out);
 FV_API int fv_sp_info(void* sp, int* start, int* len, int* seg_rows, int* groups);
 FV_API int fv_sp_forward_bf16(void* sp, void* stream, const void* q, const void* k, const void* v, void* out,
                               int out_is_bf16, float scale, int mask_mode, int block_tokens, int window, int sink);

@@ -144,6 +144,40 @@ def test_full_size_rows_wan_1p3b(fvlib, oracle):
     assert torch.equal(const, ones)
 
 
+def test_full_size_rows_wan_14b(fvlib, oracle):
+    """Config 3's shape (75 600 tokens: 295 work items of 256 rows + one of 80, 590 key tiles + one of 80 keys)
+    on 2 heads: sampled rows (item and tile edges, the tail) against the oracle over all keys; constant V."""
+    from fastvideo_rs_b200 import sdpa
+    bh, s = 2, 75600
+    q, k, v = qkv(oracle, 23, bh, s, s)
+    tq, tk, tv = to_dev_bf16(q), to_dev_bf16(k), to_dev_bf16(v)
+    out = sdpa.dense_fwd(tq, tk, tv)
+    assert sdpa.device_status() == 0
+    rows = np.unique(np.concatenate([sample_rows(s, 24, 4), [75519, 75520, 75521, 75599, 37799, 37888]])).astype(np.int32)
+    want = oracle.sdpa_rows(q, k, v, rows=rows)
+    assert_close(to_host_f32(out[:, torch.from_numpy(rows).long().cuda()]), want, "75600 rows")
+    ones = torch.full_like(tv, -0.25)
+    assert torch.equal(sdpa.dense_fwd(tq, tk, ones), ones)
+
+
+def test_full_size_chunk_causal_self_forcing(fvlib, oracle):
+    """Config 4's real shape: 32 760 tokens in 7 chunks of 4 680 (block-lower-triangular), 2 heads; rows at the
+    start, end and both sides of every chunk border against the masked oracle.  4 680 is not a multiple of the
+    128-key tile: every chunk border cuts through a key tile and through a work item."""
+    from fastvideo_rs_b200 import sdpa
+    bh, s, bt = 2, 32760, 4680
+    q, k, v = qkv(oracle, 24, bh, s, s)
+    out = sdpa.dense_fwd(to_dev_bf16(q), to_dev_bf16(k), to_dev_bf16(v), causal=sdpa.BlockCausal(bt, 0, 0))
+    assert sdpa.device_status() == 0
+    edges = [c * bt + d for c in range(1, 7) for d in (-129, -1, 0, 1, 127)]
+    rows = np.unique(np.concatenate([sample_rows(s, 16, 6), edges])).astype(np.int32)
+    want = oracle.sdpa_rows(q, k, v, rows=rows, block_causal=(bt, 0, 0))
+    assert_close(to_host_f32(out[:, torch.from_numpy(rows).long().cuda()]), want, "chunk-causal 32760")
+    # a row of chunk 0 sees chunk 0 only: equal to dense attention over the first 4 680 keys
+    first = sdpa.dense_fwd(to_dev_bf16(q[:, :bt]), to_dev_bf16(k[:, :bt]), to_dev_bf16(v[:, :bt]))
+    assert float((out[:, :bt].float() - first.float()).abs().max()) <= 2e-2
+
+
 def test_cross_attention_shape(fvlib, oracle):
     """Config 1's cross-attention: 32 760 queries over 512 text keys."""
     from fastvideo_rs_b200 import sdpa
