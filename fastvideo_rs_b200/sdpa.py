@@ -100,9 +100,16 @@ def _check_bf16_cuda(name: str, t: torch.Tensor) -> None:
 def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, plan: Plan, *, out_bf16: bool = True,
          probe: Optional[sdpa_rule.Probe] = None) -> torch.Tensor:
     """Scaled dot-product attention over BHSD q [b, h, sq, d], k / v [b, h, sk, d], as `plan` says.
-    Returns [b, h, sq, d] (bf16, or f32 with out_bf16=False).  Asynchronous on the current stream."""
+    Returns [b, h, sq, d] (bf16, or f32 with out_bf16=False).  Operands are bf16; three float32 operands are
+    rounded to bf16 first and the result comes back as float32 holding bf16-rounded values, as the reference
+    does under bf16 activations.  Mixed dtypes are an error.  Asynchronous on the current stream."""
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
         raise ValueError("sdpa expects BHSD")
+    if q.dtype == torch.float32 and k.dtype == torch.float32 and v.dtype == torch.float32:
+        # f32-stored activations: operands rounded to bf16 first, the result rounded again and handed back in
+        # the caller's storage type (act16_operands and the tail of dense, rt/sdpa.rs:167-181,206-213)
+        q16, k16, v16 = act16_operands(q, k, v)
+        return act16_widen(sdpa(q16, k16, v16, plan, out_bf16=True, probe=probe))
     for n, t in (("q", q), ("k", k), ("v", v)):
         _check_bf16_cuda(n, t)
     cs4 = ctypes.c_size_t * 4
@@ -123,6 +130,34 @@ def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, plan: Plan, *, out_b
                           ctypes.c_void_p(ws.data_ptr() if ws is not None else None),
                           ctypes.c_size_t(ws.numel() if ws is not None else 0))
     _lib.check(rc, "sdpa")
+    return out
+
+
+def act16_operands(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
+    """bf16-rounded copies of three f32 operands in one launch (act16_operands, rt/sdpa.rs:167-181)."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        if not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
+            raise ValueError(f"act16_operands: {n} must be a contiguous CUDA float32 tensor")
+    if k.shape != v.shape:
+        raise ValueError("act16_operands: k and v differ in shape")
+    outs = [torch.empty(t.shape, dtype=torch.bfloat16, device=t.device) for t in (q, k, v)]
+    fp = lambda t: ctypes.cast(ctypes.c_void_p(t.data_ptr()), ctypes.POINTER(ctypes.c_float))
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().fv_act16_operands(_stream_ptr(), fp(q), fp(k), fp(v), ctypes.c_longlong(q.numel()),
+                                          ctypes.c_longlong(k.numel()), *[ctypes.c_void_p(o.data_ptr()) for o in outs])
+    _lib.check(rc, "act16_operands")
+    return tuple(outs)
+
+
+def act16_widen(x: torch.Tensor) -> torch.Tensor:
+    """A bf16 result in f32 storage (the values stay the bf16-rounded ones)."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("act16_widen: a contiguous CUDA bf16 tensor")
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().fv_act16_widen(_stream_ptr(), ctypes.c_void_p(x.data_ptr()), ctypes.c_longlong(x.numel()),
+                                       ctypes.cast(ctypes.c_void_p(out.data_ptr()), ctypes.POINTER(ctypes.c_float)))
+    _lib.check(rc, "act16_widen")
     return out
 
 

@@ -66,21 +66,106 @@ def qk_prep(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.T
 
 
 class WanSelfAttention:
-    """forward_self without the two GEMMs: fused QKV projection in, attention out (BHSD).
+    """WanAttention without its GEMMs (wan/transformer.rs:163-445): projections in, attention out.
 
     grid: token grid in patches (frames, height, width); heads x 128 = model dim.  causal: optional
-    BlockCausal (Self-Forcing chunk-causal mask)."""
+    BlockCausal (Self-Forcing chunk-causal mask).  vsa: optional vsa.VsaCtx of the same grid -- forward_self
+    then takes the VSA route (attend_vsa) and needs the gate projection."""
 
     def __init__(self, grid, heads: int, wq: torch.Tensor, wk: torch.Tensor, eps: float = 1e-6,
-                 theta: float = 10000.0, causal: Optional[BlockCausal] = None, device="cuda"):
-        self.grid, self.heads, self.eps, self.causal = tuple(grid), heads, eps, causal
+                 theta: float = 10000.0, causal: Optional[BlockCausal] = None, device="cuda", vsa=None):
+        self.grid, self.heads, self.eps, self.causal, self.vsa = tuple(grid), heads, eps, causal, vsa
         self.wq, self.wk = wq, wk
         self.cos, self.sin = wan_rope_tables(grid, 128, theta, 0, device)
 
-    def forward_self(self, qkv: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
+    def forward_self(self, qkv: torch.Tensor, scale: Optional[float] = None, gate: Optional[torch.Tensor] = None,
+                     merged: bool = False) -> torch.Tensor:
+        """forward_self (wan/transformer.rs:265-349) between the QKV projection and the output projection.
+        qkv [batch, seq, 3 * dim] bf16; gate [batch, seq, dim] bf16 (the gate projection) with a VSA context.
+        merged: return [batch, seq, dim] (merge_heads folded into the store) instead of BHSD."""
         q, k, v = qk_prep(qkv, self.wq, self.wk, self.cos, self.sin, self.heads, eps=self.eps)
+        if self.vsa is not None:
+            if gate is None:
+                raise ValueError("forward_self: the VSA route needs the gate projection")
+            out = self.attend_vsa(q, k, v, gate)
+            return out.permute(0, 2, 1, 3).reshape(out.shape[0], out.shape[2], -1) if merged else out
+        if merged:
+            from .sdpa import dense_fwd_merged
+            return dense_fwd_merged(q, k, v, scale=scale, causal=self.causal)
         plan = Plan.block_causal(scale, self.causal) if self.causal is not None else Plan.dense(scale)
         return sdpa(q, k, v, plan)
+
+    def attend_vsa(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate_proj: torch.Tensor) -> torch.Tensor:
+        """attend_vsa (wan/transformer.rs:354-390): q, k normed and roped, v split, BHSD; the gate is the gate
+        projection split into heads with no norm and no rotation (wan/transformer.rs:336-347), linear."""
+        from . import vsa as _vsa
+        b, h, seq, d = q.shape
+        if gate_proj.shape != (b, seq, h * d):
+            raise ValueError(f"attend_vsa: gate projection {tuple(gate_proj.shape)} for {tuple(q.shape)}")
+        # head split of the gate: the prologue kernel's V path is exactly that copy
+        _, _, g = qk_prep(gate_proj, None, None, None, None, h, col_q=0, col_k=0, col_v=0, want_q=False, want_k=False)
+        out = _vsa.vsa_attention(q.view(b * h, seq, d), k.view(b * h, seq, d), v.view(b * h, seq, d), g.view(b * h, seq, d), self.vsa)
+        return out.view(b, h, seq, d)
+
+    def cross_kv(self, kv_proj: torch.Tensor, wk: Optional[torch.Tensor] = None):
+        """cross_kv (wan/transformer.rs:406-419): the text tokens' fused K|V projection [batch, text, 2 * dim] ->
+        (RMS-normed K without rotation, V), both BHSD bf16 -- the layout the attention kernel reads, computed
+        once per denoise and cached by the caller."""
+        dim = self.heads * 128
+        _, k, v = qk_prep(kv_proj, None, wk if wk is not None else self.wk, None, None, self.heads, col_q=0, col_k=0, col_v=dim,
+                          eps=self.eps, want_q=False)
+        return k, v
+
+    def forward_cross(self, q_proj: torch.Tensor, cached_kv, scale: Optional[float] = None, merged: bool = False) -> torch.Tensor:
+        """forward_cross (wan/transformer.rs:420-444): q = RMSNorm(q projection) without rotation, attention over
+        the cached text K / V.  q_proj [batch, seq, dim] bf16."""
+        q, _, _ = qk_prep(q_proj, self.wq, None, None, None, self.heads, col_q=0, col_k=0, col_v=0, eps=self.eps,
+                          want_k=False, want_v=False)
+        k, v = cached_kv
+        if merged:
+            from .sdpa import dense_fwd_merged
+            return dense_fwd_merged(q, k, v, scale=scale)
+        return sdpa(q, k, v, Plan.dense(scale))
+
+
+def ln_adaln_e(x: torch.Tensor, e: torch.Tensor, scale_slot: int, shift_slot: int, eps: float = 1e-6) -> torch.Tensor:
+    """CudaTensor::ln_adaln_e under bf16 activations (rt/fused.rs:20-70), the pass before attention:
+    x [batch, seq, dim] bf16, e [batch, e_rows, dim] f32 -> bf16(LN(x) * (1 + e[b, scale]) + e[b, shift])."""
+    if x.dtype != torch.bfloat16 or not x.is_cuda or not x.is_contiguous() or x.dim() != 3:
+        raise ValueError("ln_adaln_e: x must be a contiguous CUDA bf16 [batch, seq, dim] tensor")
+    b, seq, dim = x.shape
+    if e.dtype != torch.float32 or not e.is_cuda or not e.is_contiguous() or e.dim() != 3 or e.shape[0] != b or e.shape[2] != dim:
+        raise ValueError(f"ln_adaln_e: table {tuple(e.shape)} for {tuple(x.shape)}")
+    out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().fv_wan_ln_adaln_bf16(_stream_ptr(), ctypes.c_void_p(x.data_ptr()),
+                                             ctypes.cast(ctypes.c_void_p(e.data_ptr()), _f32p), scale_slot, shift_slot, b, seq, dim,
+                                             e.shape[1], ctypes.c_float(eps), ctypes.c_void_p(out.data_ptr()))
+    _lib.check(rc, "ln_adaln_e")
+    return out
+
+
+def self_residual_norm(hidden: torch.Tensor, attn: torch.Tensor, e: torch.Tensor, gate_slot: int, w: torch.Tensor,
+                       b: torch.Tensor, eps: float = 1e-6):
+    """wan::fuse::self_residual_norm (wan/fuse.rs:108-166), the pass after attention: returns
+    (bf16(hidden + attn * e[b, gate]), bf16(LayerNorm(that sum, unrounded) * w + b))."""
+    for n, t in (("hidden", hidden), ("attn", attn)):
+        if t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous() or t.dim() != 3:
+            raise ValueError(f"self_residual_norm: {n} must be a contiguous CUDA bf16 [batch, seq, dim] tensor")
+    bt, seq, dim = hidden.shape
+    if attn.shape != hidden.shape or e.dtype != torch.float32 or e.shape[0] != bt or e.shape[2] != dim or not e.is_contiguous():
+        raise ValueError("self_residual_norm: shapes")
+    for n, t in (("w", w), ("b", b)):
+        if t.dtype != torch.float32 or not t.is_cuda or t.numel() != dim or not t.is_contiguous():
+            raise ValueError(f"self_residual_norm: {n} must be CUDA float32 [dim]")
+    hid, normed = torch.empty_like(hidden), torch.empty_like(hidden)
+    fp = lambda t: ctypes.cast(ctypes.c_void_p(t.data_ptr()), _f32p)
+    with torch.cuda.device(hidden.device):
+        rc = _lib.lib().fv_wan_self_residual_norm_bf16(_stream_ptr(), ctypes.c_void_p(hidden.data_ptr()), ctypes.c_void_p(attn.data_ptr()),
+                                                       fp(e), gate_slot, fp(w), fp(b), bt, seq, dim, e.shape[1], ctypes.c_float(eps),
+                                                       ctypes.c_void_p(hid.data_ptr()), ctypes.c_void_p(normed.data_ptr()))
+    _lib.check(rc, "self_residual_norm")
+    return hid, normed
 
 
 class HostStaged:

@@ -204,6 +204,18 @@ FV_API int fv_wan_rope_tables(int ppf, int pph, int ppw, int d, double theta, in
  * vsa_attention_device (:358-470) with its launchers (rt/ops.rs:811-923,1074-1383,1554-1619;
  * rt/attn_dc.rs:275-604); arithmetic of the host twin vsa_attention_host (rt/vsa.rs:116-262). */
 
+/* ---- operand rounding for f32-stored activations ------------------------------------------------
+ * The reference rounds q, k, v to bf16 before its attention kernels under bf16 activations and rounds the
+ * result again (act16_operands and the tail of dense, crates/fastvideo-cudarc/src/rt/sdpa.rs:167-181,184-214:
+ * three cast launches before, one after).  A host whose tensors are f32 enters here:
+ * fv_act16_operands rounds all three operands (RNE) in ONE launch into caller-provided bf16 buffers
+ * (q_count and kv_count are value counts; k and v have kv_count each); the attention entries then run on
+ * those; fv_act16_widen widens a bf16 result back to f32 storage, so the values the host sees are the
+ * bf16-rounded ones the reference returns.  Pointers 16-byte aligned.  Declines: empty sizes. */
+FV_API int fv_act16_operands(void* stream, const float* q, const float* k, const float* v, long long q_count,
+                             long long kv_count, void* q16, void* k16, void* v16);
+FV_API int fv_act16_widen(void* stream, const void* src16, long long count, float* dst);
+
 /* ---- the block glue either side of self-attention (bf16 activations) ---------------------------------
  * e: the block's AdaLN table, f32 [batch, e_rows, dim] (6 rows in Wan: shift/scale/gate of attention and FFN);
  * hidden rows are [batch * seq, dim] bf16, dim a multiple of 8, at most 6 144.  Both are one pass over HBM: a

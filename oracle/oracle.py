@@ -318,5 +318,29 @@ def vsa_attention_host(q, k, v, gate, grid, topk, scale=None, want_aux=False):
     return (out, sel, sc, co) if want_aux else out
 
 
+# --------------------------------------------------------------------------- block glue
+def ln_adaln_e(x, e, scale_slot: int, shift_slot: int, eps: float = 1e-6) -> np.ndarray:
+    """Unaffine LayerNorm + AdaLN modulation, f32 (C/rt/kernels/act16.cu:184-209, mx_ln_adaln_e):
+    x [batch, seq, dim], e [batch, e_rows, dim] -> (x - mean) * rsqrt(var + eps) * (1 + e[b, scale]) + e[b, shift],
+    biased variance of the deviations from the mean.  The bf16 kernel rounds this once."""
+    x, e = _f32(x), _f32(e)
+    mean = x.mean(axis=-1, keepdims=True, dtype=np.float32)
+    d = x - mean
+    inv = (1.0 / np.sqrt((d * d).mean(axis=-1, keepdims=True, dtype=np.float32) + np.float32(eps))).astype(np.float32)
+    return (d * inv) * (np.float32(1.0) + e[:, scale_slot][:, None, :]) + e[:, shift_slot][:, None, :]
+
+
+def self_residual_norm(h, attn, e, gate_slot: int, w, b, eps: float = 1e-6):
+    """wan_res_ln with res_mode 0 / ln_mode 0 (C/wan/kernels/block.cu:17-78; host twin C/wan/fuse.rs:108-166):
+    s = h + attn * e[b, gate] in f32; returns (bf16(s), LN(s) * w + b) -- the norm reads the UNROUNDED s; the
+    kernel rounds the second once."""
+    h, attn, e, w, b = _f32(h), _f32(attn), _f32(e), _f32(w), _f32(b)
+    s = h + attn * e[:, gate_slot][:, None, :]
+    mean = s.mean(axis=-1, keepdims=True, dtype=np.float32)
+    d = s - mean
+    inv = (1.0 / np.sqrt((d * d).mean(axis=-1, keepdims=True, dtype=np.float32) + np.float32(eps))).astype(np.float32)
+    return bf16_round(s), (d * inv) * w + b
+
+
 def num_threads() -> int:
     return lib().fvo_num_threads()

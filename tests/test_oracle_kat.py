@@ -251,3 +251,30 @@ def test_qk_norm_rope_matches_definition(oracle):
     # the statistic spans all heads: per-head differs
     per = oracle.qk_norm_rope_bhsd(src, w, None, None, b, seq, heads, d, width, heads * d, 1e-6, per_head=True)
     assert np.abs(per - plain).max() > 1e-3
+
+
+def test_block_glue_twins_closed_form(oracle):
+    """The restatements of ln_adaln_e (C/rt/kernels/act16.cu:184-209) and of the fused residual + norm
+    (C/wan/kernels/block.cu:17-78) on inputs whose answer is known in closed form: a zero AdaLN table leaves a
+    plain LayerNorm (zero mean, unit variance), scale / shift rows act as (1 + s) and + t, a zero gate leaves the
+    hidden state as it was, and the norm of the residual reads the UNROUNDED sum (a sum that rounds to a
+    constant row still has a non-zero normalised output)."""
+    x = oracle.seeded_normal(5, 0, (2, 9, 64))
+    e = np.zeros((2, 6, 64), np.float32)
+    y = oracle.ln_adaln_e(x, e, 1, 0)
+    assert np.abs(y.mean(-1)).max() < 1e-6 and np.abs(y.var(-1) - 1.0).max() < 1e-4
+    e[:, 1] = 0.5
+    e[:, 0] = -2.0
+    assert np.allclose(oracle.ln_adaln_e(x, e, 1, 0), y * 1.5 - 2.0, atol=1e-6)
+    h = oracle.bf16_round(x)
+    a = oracle.bf16_round(oracle.seeded_normal(5, 1, (2, 9, 64)))
+    w, b = np.full(64, 2.0, np.float32), np.full(64, 0.25, np.float32)
+    hid, normed = oracle.self_residual_norm(h, a, np.zeros((2, 6, 64), np.float32), 2, w, b)
+    assert np.array_equal(hid, h)
+    assert np.allclose(normed, 2.0 * oracle.ln_adaln_e(h, np.zeros((2, 6, 64), np.float32), 0, 0) + 0.25, atol=1e-5)
+    # unrounded sum: h = 1 everywhere, attn * gate = tiny alternating values that vanish in bf16(h + .)
+    h1 = np.ones((1, 1, 64), np.float32)
+    a1 = (np.where(np.arange(64) % 2 == 0, 1.0, -1.0) * 2.0 ** -12).astype(np.float32).reshape(1, 1, 64)
+    g = np.ones((1, 6, 64), np.float32)
+    hid1, n1 = oracle.self_residual_norm(h1, a1, g, 2, np.ones(64, np.float32), np.zeros(64, np.float32))
+    assert np.array_equal(hid1, h1) and np.abs(n1).min() > 0.2  # 2^-12 / sqrt(2^-24 + eps)

@@ -46,7 +46,7 @@ def _case(oracle, seed, bh, sq, lens):
     return q, k, v, k_all, v_all, starts, rows
 
 
-def _run_both(fvlib, oracle, seed, bh, sq, lens, local):
+def _run_both(fvlib, oracle, seed, bh, sq, lens, local, check_memory=False):
     q, k, v, k_all, v_all, starts, rows = _case(oracle, seed, bh, sq, lens)
     tq, tk, tv = to_dev_bf16(q), to_dev_bf16(k_all), to_dev_bf16(v_all)
     scale = ctypes.c_float(1.0 / math.sqrt(128))
@@ -60,11 +60,20 @@ def _run_both(fvlib, oracle, seed, bh, sq, lens, local):
     out = torch.full((bh, sq, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
     k_loc, v_loc = tk[local].contiguous(), tv[local].contiguous()
     lens2 = [n if s != local else 0 for s, n in enumerate(lens)]
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
     rc = fvlib.fv_sdpa_two_pass_noalloc_bf16(stream, _vp(tq), _vp(k_loc), _vp(v_loc), lens[local], starts[local], rows,
                                              _vp(tk), _vp(tv), len(lens), _i32(lens2), _i32(starts), rows, _vp(out), 1,
                                              bh, sq, scale, None)
     assert rc == 0, fvlib.fv_last_error()
-    torch.cuda.synchronize()
+    # the status word the call's kernels report to is the library's own: a wait that ran out inside this call
+    # would show here, and reading it allocates nothing either
+    code = ctypes.c_int(-1)
+    assert fvlib.fv_device_status(stream, ctypes.byref(code)) == 0, fvlib.fv_last_error()
+    assert code.value == 0
+    if check_memory:
+        # cudaMemGetInfo around a warm call (the module image was loaded by the call before it): not one byte
+        assert torch.cuda.mem_get_info()[0] == free_before
     got, want = to_host_f32(out), to_host_f32(ref)
     assert np.isfinite(got).all()
     err = np.abs(got - want)
@@ -79,7 +88,27 @@ def test_no_alloc_entry_matches_the_existing_entry_twice_in_a_row(fvlib, oracle)
     # first call: 3 segments, the middle one local; second call right after it: other sizes, other data,
     # the first segment local -- it reuses the built-in array the first call wrote
     _run_both(fvlib, oracle, 901, 3, 300, [334, 333, 333], local=1)
-    _run_both(fvlib, oracle, 902, 2, 513, [200, 457], local=0)
+    _run_both(fvlib, oracle, 902, 2, 513, [200, 457], local=0, check_memory=True)
+
+
+def test_a_wait_that_runs_out_is_seen_after_a_no_alloc_call(fvlib, oracle):
+    """The status word is shared: a kernel that gave up before the call (the wait self-test, one warp, a
+    barrier nobody arrives at, 1e5 cycles) is still reported by the status read that follows the call."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    fvlib.fv_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_longlong]
+    assert fvlib.fv_selftest_wait_timeout(stream, 100000) == 0, fvlib.fv_last_error()
+    q, k, v, k_all, v_all, starts, rows = _case(oracle, 903, 1, 128, [128, 128])
+    tq, tk, tv = to_dev_bf16(q), to_dev_bf16(k_all), to_dev_bf16(v_all)
+    out = torch.empty((1, 128, 128), dtype=torch.bfloat16, device="cuda")
+    rc = fvlib.fv_sdpa_two_pass_noalloc_bf16(stream, _vp(tq), _vp(tk[0]), _vp(tv[0]), 128, 0, rows, _vp(tk), _vp(tv), 2,
+                                             _i32([0, 128]), _i32(starts), rows, _vp(out), 1, 1, 128,
+                                             ctypes.c_float(1.0 / math.sqrt(128)), None)
+    assert rc == 0, fvlib.fv_last_error()
+    code = ctypes.c_int(0)
+    assert fvlib.fv_device_status(stream, ctypes.byref(code)) != 0
+    assert code.value == 109
+    assert fvlib.fv_device_status(stream, ctypes.byref(code)) == 0 and code.value == 0   # read once, cleared
+    assert np.isfinite(to_host_f32(out)).all()
 
 
 def test_no_alloc_entry_refuses_calls_beyond_its_built_in_scratch(fvlib):
