@@ -128,7 +128,23 @@ struct Job {
     int heavy_first;         // items of a plane from the last query block to the first
     int q_div;               // > 1: split-KV, plane i of k / v / out reads plane i / q_div of q
     long long wait_cycles;   // budget of every bounded wait
+#ifdef FV_ATT_TRACE
+    unsigned long long* trace;  // bring-up builds only: [3 roles][trace_steps][8] SM clock stamps of CTA 0
+    int trace_steps;
+#endif
 };
+
+// Bring-up instrumentation, compiled only with -DFV_ATT_TRACE (never in the shipped library): CTA 0's
+// issuer (role 2) and lane 0 of the first softmax warp of each row tile (roles 0, 1) stamp the SM clock.
+#ifdef FV_ATT_TRACE
+#define FV_TR(jb, role, step, ev)                                                                       \
+    do {                                                                                                \
+        if (blockIdx.x == 0 && (jb).trace && (int)(step) < (jb).trace_steps)                            \
+            (jb).trace[(((size_t)(role) * (jb).trace_steps) + (step)) * 8 + (ev)] = (unsigned long long)clock64(); \
+    } while (0)
+#else
+#define FV_TR(jb, role, step, ev) do { } while (0)
+#endif
 
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL) || !defined(__CUDA_ARCH__)
 
@@ -353,7 +369,8 @@ FV_DEV void exp32(const uint32_t (&u)[32], uint32_t* pw, uint64_t s2, uint64_t n
     for (int w = 0; w < 16; w++) {
         float t0, t1, p0, p1;
         unpack_f32x2(fma_f32x2(pack_f32x2(as_f(u[2 * w]), as_f(u[2 * w + 1])), s2, nf), t0, t1);
-        if (POLY && FV_ATT_POLY > 0 && (w % FV_ATT_POLY) == FV_ATT_POLY - 1) {
+        constexpr int kEvery = FV_ATT_POLY > 0 ? FV_ATT_POLY : 1;
+        if (POLY && FV_ATT_POLY > 0 && (w % kEvery) == kEvery - 1) {
             top = max3(top, t0, t1);
             ex2_poly_x2(t0, t1, p0, p1);
         } else {
@@ -553,6 +570,8 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
             if (!__all_sync(kFullWarp, wait(bt + Smem::s_ready, s_count & 1u))) return;
             s_count++;
             tc_fence_after();
+            const bool tr = quad == 0 && lane == 0;
+            if (tr) FV_TR(jb, tile, s_count - 1u, 0);
 
             Cols cols{0, kt.valid, 0, kt.valid == kKeyTile};
             if constexpr (MASKED) {
@@ -568,15 +587,20 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
                 uint32_t ua[32], ub[32], pw[32];
                 load_half(tS, ua, ub);
                 land_half(ua, ub);
+                if (tr) FV_TR(jb, tile, s_count - 1u, 1);
                 const float sum0 = half_exp<true>(ua, ub, sl2, -rs.m, pw);
+                if (tr) FV_TR(jb, tile, s_count - 1u, 2);
                 load_half(tS + 64u, ua, ub);  // on its way while the first half is handed over
                 if (__any_sync(kFullWarp, !(sum0 <= kGuard))) {
                     land_half(ua, ub);        // (nothing may be in flight into registers when the call is made)
                     hot = false;              // nothing of this tile is stored: the careful way, whole tile
                 } else {
                     hand_over(tS, 0u, pw, bt + Smem::p_early, lane);
+                    if (tr) FV_TR(jb, tile, s_count - 1u, 3);
                     land_half(ua, ub);
+                    if (tr) FV_TR(jb, tile, s_count - 1u, 4);
                     const float sum1 = half_exp<true>(ua, ub, sl2, -rs.m, pw);
+                    if (tr) FV_TR(jb, tile, s_count - 1u, 5);
                     if (__any_sync(kFullWarp, !(sum1 <= kGuard))) {
                         // The first half went out against the old reference and its product may be running:
                         // wait for it (the issuer signals every early product), then the careful way for the
@@ -587,6 +611,7 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
                         careful_tile(tS, tO, bt, cols, sl2, true, true, lane, &rs);
                     } else {
                         hand_over(tS, 32u, pw, bt + Smem::p_ready, lane);
+                        if (tr) FV_TR(jb, tile, s_count - 1u, 6);
                         rs.l += sum0 + sum1;
                     }
                 }
@@ -723,14 +748,16 @@ FV_DEV uint32_t kv_slot_addr(uint32_t sbase, uint32_t c) { return sbase + Smem::
 // previous item have finished reading it by the time they have stored any of the new item's P.
 // (An issuer that serves the two row tiles out of order, probing their barriers without blocking, was
 // tried: its probes compete with the MMAs' operand reads for shared memory and it ran 23 % slower.)
-FV_DEV bool issue_output(uint32_t sbase, uint32_t t, uint32_t tmem, uint64_t vd, bool fresh, uint32_t pc,
+FV_DEV bool issue_output(const Job& jb, uint32_t sbase, uint32_t t, uint32_t tmem, uint64_t vd, bool fresh, uint32_t pc,
                          const Waiter& wait) {
     const uint32_t bt = sbase + 8u * t, tO = tmem + tmem_output(t), tP = tmem + tmem_scores(t);
     if (!wait(bt + Smem::p_early, pc & 1u)) return false;
+    FV_TR(jb, 2, pc, 1 + 3 * t);
     tc_fence_after();
     output_mma_early(tO, tP, vd, fresh);
     umma_commit(bt + Smem::pv_early);
     if (!wait(bt + Smem::p_ready, pc & 1u)) return false;
+    FV_TR(jb, 2, pc, 2 + 3 * t);
     tc_fence_after();
     output_mma_late(tO, tP, vd);
     return true;
@@ -768,11 +795,12 @@ FV_DEV void issuer_thread(const Job& jb, uint32_t sbase, uint32_t tmem, const Wa
                 if (!wait(sbase + Smem::kv_full + 8u * ((kc - 1u) % kKvSlots), ((kc - 1u) / kKvSlots) & 1u)) { ok = false; break; }
                 vd = umma_desc_sw128(kv_slot_addr(sbase, kc - 1u), kPanelBytes, 1024);
                 tc_fence_after();
+                FV_TR(jb, 2, pc, 0);
             }
             if (j < n) kd = umma_desc_sw128(kv_slot_addr(sbase, kc), 16, 1024);
 #pragma unroll
             for (uint32_t t = 0; t < 2; t++) {
-                if (j > 0 && !issue_output(sbase, t, tmem, vd, j == 1, pc, wait)) { ok = false; break; }
+                if (j > 0 && !issue_output(jb, sbase, t, tmem, vd, j == 1, pc, wait)) { ok = false; break; }
                 if (j == n) {
                     umma_commit(sbase + Smem::o_ready + 8u * t);
                     continue;
@@ -787,6 +815,7 @@ FV_DEV void issuer_thread(const Job& jb, uint32_t sbase, uint32_t tmem, const Wa
                 }
                 scores_mma(tmem + tmem_scores(t), t ? qd_b : qd_a, kd);
                 umma_commit(sbase + Smem::s_ready + 8u * t);
+                if (j > 0) FV_TR(jb, 2, pc, 3 + 3 * t);
                 if (j == n - 1) umma_commit(sbase + Smem::q_free + 8u * (t ? qb : qa));
             }
             if (!ok) break;

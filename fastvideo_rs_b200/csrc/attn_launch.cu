@@ -53,6 +53,15 @@ struct LaunchArgs {
     int q_split = 0, q_row1 = 0;
 };
 
+#ifdef FV_ATT_TRACE
+static unsigned long long* g_fv_trace = nullptr;
+static int g_fv_trace_steps = 0;
+extern "C" __attribute__((visibility("default"))) void fv_debug_set_trace(unsigned long long* dev_buf, int steps) {
+    g_fv_trace = dev_buf;
+    g_fv_trace_steps = steps;
+}
+#endif
+
 static int launch(cudaStream_t stream, const LaunchArgs& a) {
     int dev;
     int rc = fvrt::require_sm100(&dev);
@@ -107,6 +116,10 @@ static int launch(cudaStream_t stream, const LaunchArgs& a) {
     jb.heavy_first = masked ? 1 : 0;
     jb.q_div = a.q_div;
     jb.wait_cycles = FV_WAIT_CYCLES;
+#ifdef FV_ATT_TRACE
+    jb.trace = g_fv_trace;
+    jb.trace_steps = g_fv_trace_steps;
+#endif
     rc = fvrt::status_word(dev, &jb.status);
     if (rc != FV_RAN) return rc;
     const long long items = (long long)jb.q_blocks * a.planes;

@@ -10,7 +10,6 @@
 // y = (x*inv)*w, even = y0*cos[s,even] - y1*sin[s,even+1], odd = y0*sin[s,even+1] + y1*cos[s,even],
 // every product and sum rounded separately (no fused multiply-add), then one rounding to bf16.
 // Only the sum of squares differs: fused multiply-adds in a tree instead of a sequential sum of rounded squares.
-#include "fv_ptx.cuh"
 #include "fv_runtime.h"
 #include <cuda_bf16.h>
 #include <math.h>
@@ -162,185 +161,155 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_kernel(const Params
 }
 
 
-// ---- the same arithmetic behind a ring of staged rows -----------------------------------------------
-// One CTA per row pays the whole DRAM round trip once per row with nothing else in flight.  Here a
-// CTA is persistent: it walks rows blockIdx.x, + gridDim.x, ... and keeps `stages` of them in flight
-// as bulk copies (q, k, v column ranges of the projection row and the row's cos / sin) into a ring
-// in shared memory, each stage completing on an mbarrier.  The block reduction's barrier doubles as
-// "every thread has read its part of the stage", after which one thread refills it.  The norm
-// weights stay in registers for the CTA's lifetime.  Values and rounding are those of the kernel
-// above, bit for bit (same reduction tree).
-struct RingGeom {
-    int stages;
-    uint32_t off_k, off_v, off_cos, off_sin;  // byte offsets inside a stage (q at 0)
-    uint32_t stage_bytes;
-    long long rows;                            // batch * seq
-    int* status;
-};
-
-template <int MAXT, int MINB>
-__global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_ring_kernel(const Params p, const RingGeom g) {
-    using namespace fvp;
-    extern __shared__ __align__(128) unsigned char ring_smem[];
-    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = blockDim.x >> 5;
-    const bool act = t < p.heads * 16;
-    const int h = act ? (8 * t) / kD : 0, pd = act ? (8 * t) % kD : 0;
-    const uint32_t dimB = (uint32_t)p.heads * kD * 2u;
-    const uint32_t base = smem_u32(ring_smem);
-    const uint32_t bars = base + (uint32_t)g.stages * g.stage_bytes;
-    unsigned char* tail = ring_smem + (size_t)g.stages * g.stage_bytes + 8 * g.stages;
-    float* red = reinterpret_cast<float*>(tail);                       // [2][2 * nwarps]
-    volatile int* abort_ptr = reinterpret_cast<volatile int*>(tail + 16 * nwarps);
-
-    if (t == 0) {
-        for (int s = 0; s < g.stages; s++) mbar_init(bars + 8 * s, 1);
-        *abort_ptr = (*(volatile int*)g.status != FV_ST_OK) ? 1 : 0;
-        mbar_init_fence();
-    }
-    __syncthreads();
-    if (*abort_ptr) return;  // CTA-uniform
-    const WaitCtl ctl{abort_ptr, g.status, 7};
-
-    uint32_t row_bytes = 0;
-    if (p.q_out) row_bytes += dimB;
-    if (p.k_out) row_bytes += dimB;
-    if (p.v_out) row_bytes += dimB;
-    if (p.cosv) row_bytes += 2u * kD * 4u;
-    auto issue = [&](long long row, int srow, int s) {  // one thread; srow = row % seq
-        const uint32_t dst = base + (uint32_t)s * g.stage_bytes, bar = bars + 8 * s;
-        const __nv_bfloat16* src = p.proj + (size_t)row * p.width;
-        mbar_expect_tx(bar, row_bytes);
-        if (p.q_out) bulk_load(dst, src + p.col_q, dimB, bar);
-        if (p.k_out) bulk_load(dst + g.off_k, src + p.col_k, dimB, bar);
-        if (p.v_out) bulk_load(dst + g.off_v, src + p.col_v, dimB, bar);
-        if (p.cosv) {
-            const size_t sidx = (size_t)srow * kD;
-            bulk_load(dst + g.off_cos, p.cosv + sidx, kD * 4u, bar);
-            bulk_load(dst + g.off_sin, p.sinv + sidx, kD * 4u, bar);
-        }
-    };
-    // Row indices advance by gridDim.x; (batch, position) follow by subtraction, the ring slot and its
-    // phase by counting: no division inside the loop.
-    const int step = (int)gridDim.x;
-    auto advance = [&](int& b, int& srow) {
-        srow += step;
-        while (srow >= p.seq) {
-            srow -= p.seq;
-            b++;
-        }
-    };
-    long long issued = 0;                    // rows of this CTA handed to the copy unit (thread 0 only)
-    long long nrow = (long long)blockIdx.x;  // next row to hand over, its batch and position, its slot
-    int nb = (int)(blockIdx.x / (unsigned)p.seq), nsrow = (int)(blockIdx.x % (unsigned)p.seq), nslot = 0;
-    if (t == 0) {
-        for (; nslot < g.stages && nrow < g.rows; nslot++) {
-            issue(nrow, nsrow, nslot);
-            issued++;
-            nrow += step;
-            advance(nb, nsrow);
-        }
-    }
-
-    float wqv[8], wkv[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) wqv[i] = wkv[i] = 0.f;
-    if (act && p.q_out) {
-        const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.wq + 8 * t)), w1 = __ldg(reinterpret_cast<const float4*>(p.wq + 8 * t + 4));
-        wqv[0] = w0.x; wqv[1] = w0.y; wqv[2] = w0.z; wqv[3] = w0.w; wqv[4] = w1.x; wqv[5] = w1.y; wqv[6] = w1.z; wqv[7] = w1.w;
-    }
-    if (act && p.k_out) {
-        const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.wk + 8 * t)), w1 = __ldg(reinterpret_cast<const float4*>(p.wk + 8 * t + 4));
-        wkv[0] = w0.x; wkv[1] = w0.y; wkv[2] = w0.z; wkv[3] = w0.w; wkv[4] = w1.x; wkv[5] = w1.y; wkv[6] = w1.z; wkv[7] = w1.w;
-    }
+// ---- the same arithmetic with a group of warps per row, rows held in registers ------------------------
+// A group of G warps (G = 1, 2 or 4 by row width) owns a row; thread g of the group holds the 8-value
+// chunks g, g + 32 G, g + 64 G, ... of q and of k as packed bf16 (J chunks each, 16-byte loads, all issued
+// before anything is used; v's chunks are requested first and stored as they arrive).  Groups are
+// independent: the only synchronisation is one named barrier among the G warps of a group per row, for the
+// exchange of the per-warp partial sums.  Several groups per CTA and several CTAs per SM keep enough rows
+// in flight to cover the memory latency without a staging ring, a copy unit or a wait that could run out.
+// The reduction tree is the row kernel's, bit for bit: chunk c is that kernel's thread c, so warp gw of the
+// group holds, in its iteration j, exactly the 32 partials of that kernel's warp gw + G j in the same lanes;
+// the butterflies and the exchange through red[] are the same.
+template <int J, int G, int NG, int MINB>
+__global__ void __launch_bounds__(32 * G * NG, MINB) fv_wan_qk_prep_group_kernel(const Params p, long long rows) {
+    __shared__ float red[2][NG][2][32];
+    const int t = threadIdx.x, lane = t & 31;
+    const int grp = t / (32 * G), g = t % (32 * G), gw = g >> 5;
+    const int chunks = p.heads * 16, nwarps = (chunks + 31) >> 5;
+    const int pd = 8 * (g & 15);  // (8 c) % 128 is the same for every chunk of a thread: 32 G is a multiple of 16
     const float denom = p.per_head ? (float)kD : (float)(p.heads * kD);
     const int span = p.per_head ? 16 : 32;
-
-    long long i = 0;
-    bool failed = false;
-    int b = (int)(blockIdx.x / (unsigned)p.seq), srow = (int)(blockIdx.x % (unsigned)p.seq);
-    int s = 0;
-    uint32_t ph = 0;
-    for (long long row = (long long)blockIdx.x; row < g.rows; row += step, i++) {  // CTA-uniform trip count
-        const bool ok = mbar_wait(bars + 8 * s, ph, ctl);
-        const unsigned char* st = ring_smem + (size_t)s * g.stage_bytes;
-        float xq[8], xk[8];
+    const long long stride = (long long)gridDim.x * NG;
+    int it = 0;
+    for (long long row = (long long)blockIdx.x * NG + grp; row < rows; row += stride, it ^= 1) {
+        const int b = (int)(row / p.seq), s = (int)(row % p.seq);
+        const __nv_bfloat16* src = p.proj + (size_t)row * p.width;
+        uint4 vq[J], vk[J];
+        if (p.v_out) {
+            uint4 vv[J];
 #pragma unroll
-        for (int j = 0; j < 8; j++) xq[j] = xk[j] = 0.f;
+            for (int j = 0; j < J; j++) {
+                const int c = g + 32 * G * j;
+                if (c < chunks) vv[j] = __ldcs(reinterpret_cast<const uint4*>(src + p.col_v + 8 * c));
+            }
+#pragma unroll
+            for (int j = 0; j < J; j++) {
+                const int c = g + 32 * G * j;
+                vq[j] = make_uint4(0u, 0u, 0u, 0u);
+                if (p.q_out && c < chunks) vq[j] = __ldcs(reinterpret_cast<const uint4*>(src + p.col_q + 8 * c));
+            }
+#pragma unroll
+            for (int j = 0; j < J; j++) {
+                const int c = g + 32 * G * j;
+                vk[j] = make_uint4(0u, 0u, 0u, 0u);
+                if (p.k_out && c < chunks) vk[j] = __ldcs(reinterpret_cast<const uint4*>(src + p.col_k + 8 * c));
+            }
+#pragma unroll
+            for (int j = 0; j < J; j++) {
+                const int c = g + 32 * G * j;
+                if (c < chunks)
+                    *reinterpret_cast<uint4*>(p.v_out + (((size_t)b * p.heads + (c >> 4)) * p.seq + s) * kD + pd) = vv[j];
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < J; j++) {
+                const int c = g + 32 * G * j;
+                vq[j] = vk[j] = make_uint4(0u, 0u, 0u, 0u);
+                if (p.q_out && c < chunks) vq[j] = __ldcs(reinterpret_cast<const uint4*>(src + p.col_q + 8 * c));
+                if (p.k_out && c < chunks) vk[j] = __ldcs(reinterpret_cast<const uint4*>(src + p.col_k + 8 * c));
+            }
+        }
         float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
-        uint4 vv = make_uint4(0u, 0u, 0u, 0u);
-        float sq = 0.f, sk = 0.f;
-        if (ok && act) {
-            if (p.q_out) {
-                unpack8(*reinterpret_cast<const uint4*>(st + 16 * t), xq);
-                sq = sumsq8(xq, sq);
-            }
-            if (p.k_out) {
-                unpack8(*reinterpret_cast<const uint4*>(st + g.off_k + 16 * t), xk);
-                sk = sumsq8(xk, sk);
-            }
-            if (p.v_out) vv = *reinterpret_cast<const uint4*>(st + g.off_v + 16 * t);
-            if (p.cosv) {
-                const float4* cp = reinterpret_cast<const float4*>(st + g.off_cos + 4 * pd);
-                const float4* sp = reinterpret_cast<const float4*>(st + g.off_sin + 4 * pd);
-                const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
-                cs[0] = c0.x; cs[1] = c0.z; cs[2] = c1.x; cs[3] = c1.z;
-                sn[0] = s0.y; sn[1] = s0.w; sn[2] = s1.y; sn[3] = s1.w;
-            }
+        if (p.cosv) {
+            const float4* cp = reinterpret_cast<const float4*>(p.cosv + (size_t)s * kD + pd);
+            const float4* sp = reinterpret_cast<const float4*>(p.sinv + (size_t)s * kD + pd);
+            const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+            cs[0] = c0.x; cs[1] = c0.z; cs[2] = c1.x; cs[3] = c1.z;
+            sn[0] = s0.y; sn[1] = s0.w; sn[2] = s1.y; sn[3] = s1.w;
         }
-        lanes_sum(sq, sk, span);
-        float* rb = red + (i & 1) * 2 * nwarps;
-        if (lane == 0) {
-            rb[warp] = sq;
-            rb[nwarps + warp] = sk;
-        }
-        // One barrier per row: the reduction's, the verdict on the wait, and the release of stage s.
-        if (!__syncthreads_and(ok ? 1 : 0)) {
-            failed = true;
-            break;  // CTA-uniform
-        }
-        if (t == 0 && nrow < g.rows) {  // the slot just read is the next one to fill
-            issue(nrow, nsrow, s);
-            issued++;
-            nrow += step;
-            advance(nb, nsrow);
-        }
-        if (!p.per_head) warps_sum(rb, nwarps, lane, sq, sk);
-        const size_t dst = (((size_t)b * p.heads + h) * p.seq + srow) * kD + pd;
-        advance(b, srow);
-        if (++s == g.stages) {
-            s = 0;
-            ph ^= 1u;
-        }
-        if (!act) continue;
-        if (p.v_out) *reinterpret_cast<uint4*>(p.v_out + dst) = vv;
-        auto finish = [&](const float (&x)[8], float ss, const float (&wv)[8], __nv_bfloat16* out) {
-            const float ms = __fdiv_rn(ss, denom);
-            const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, p.eps)));
-            float y[8];
+        // per-chunk sums of squares, then the row kernel's butterflies warp by warp
+        float sq[J], sk[J];
 #pragma unroll
-            for (int j = 0; j < 8; j++) y[j] = __fmul_rn(__fmul_rn(x[j], inv), wv[j]);
-            float o[8];
-            if (p.cosv) {
+        for (int j = 0; j < J; j++) {
+            float x[8];
+            unpack8(vq[j], x);
+            sq[j] = sumsq8(x, 0.f);
+            unpack8(vk[j], x);
+            sk[j] = sumsq8(x, 0.f);
+        }
 #pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                    const float c = cs[j >> 1], sv = sn[j >> 1];
-                    o[j] = __fsub_rn(__fmul_rn(y[j], c), __fmul_rn(y[j + 1], sv));
-                    o[j + 1] = __fadd_rn(__fmul_rn(y[j], sv), __fmul_rn(y[j + 1], c));
+        for (int j = 0; j < J; j++) lanes_sum(sq[j], sk[j], span);
+        float tq = 0.f, tk = 0.f;
+        if (!p.per_head) {
+            float* rb = &red[it][grp][0][0];
+            if (lane == 0) {
+#pragma unroll
+                for (int j = 0; j < J; j++) {
+                    const int w = gw + G * j;
+                    if (w < 32) {
+                        rb[w] = sq[j];
+                        rb[32 + w] = sk[j];
+                    }
                 }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; j++) o[j] = y[j];
             }
-            *reinterpret_cast<uint4*>(out + dst) =
-                make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
-        };
-        if (p.q_out) finish(xq, sq, wqv, p.q_out);
-        if (p.k_out) finish(xk, sk, wkv, p.k_out);
+            if (G == 1) __syncwarp();
+            else asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(32 * G) : "memory");
+            tq = lane < nwarps ? rb[lane] : 0.f;
+            tk = lane < nwarps ? rb[32 + lane] : 0.f;
+            lanes_sum(tq, tk, 32);
+        }
+#pragma unroll
+        for (int j = 0; j < J; j++) {
+            const int c = g + 32 * G * j;
+            if (c >= chunks) continue;
+            const size_t dst = (((size_t)b * p.heads + (c >> 4)) * p.seq + s) * kD + pd;
+            auto finish = [&](const uint4& raw, float ss, const float* wsrc, __nv_bfloat16* out) {
+                float x[8];
+                unpack8(raw, x);
+                const float4 w0 = __ldg(reinterpret_cast<const float4*>(wsrc + 8 * c)), w1 = __ldg(reinterpret_cast<const float4*>(wsrc + 8 * c + 4));
+                const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                const float ms = __fdiv_rn(ss, denom);
+                const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, p.eps)));
+                float y[8], o[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) y[i] = __fmul_rn(__fmul_rn(x[i], inv), wv[i]);
+                if (p.cosv) {
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2) {
+                        const float cc = cs[i >> 1], sv = sn[i >> 1];
+                        o[i] = __fsub_rn(__fmul_rn(y[i], cc), __fmul_rn(y[i + 1], sv));
+                        o[i + 1] = __fadd_rn(__fmul_rn(y[i], sv), __fmul_rn(y[i + 1], cc));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) o[i] = y[i];
+                }
+                *reinterpret_cast<uint4*>(out + dst) =
+                    make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
+            };
+            if (p.q_out) finish(vq[j], p.per_head ? sq[j] : tq, p.wq, p.q_out);
+            if (p.k_out) finish(vk[j], p.per_head ? sk[j] : tk, p.wk, p.k_out);
+        }
     }
-    // A wait ran out: copies already handed to the copy unit must land before the ring goes away.
-    if (failed && t == 0) {
-        for (long long j = i; j < issued; j++)
-            if (!mbar_drain(bars + 8 * (uint32_t)(j % g.stages), (uint32_t)((j / g.stages) & 1))) break;
+}
+
+template <int G, int NG>
+int launch_group(const Params& p, long long rows, int j_need, int sms, cudaStream_t stream) {
+    auto go = [&](auto kern, int per_sm) -> int {
+        long long grid = (long long)sms * per_sm;
+        const long long need = (rows + NG - 1) / NG;
+        if (grid > need) grid = need;
+        kern<<<(unsigned)grid, 32 * G * NG, 0, stream>>>(p, rows);
+        FV_CUDA(cudaGetLastError());
+        return FV_RAN;
+    };
+    switch (j_need) {
+        case 1: return go(fv_wan_qk_prep_group_kernel<1, G, NG, 4>, 4);
+        case 2: return go(fv_wan_qk_prep_group_kernel<2, G, NG, 4>, 4);
+        case 3: return go(fv_wan_qk_prep_group_kernel<3, G, NG, 2>, 2);
+        case 4: return go(fv_wan_qk_prep_group_kernel<4, G, NG, 2>, 2);
+        default: return go(fv_wan_qk_prep_group_kernel<5, G, NG, 2>, 2);
     }
 }
 
@@ -387,39 +356,22 @@ extern "C" int fv_wan_qk_prep_bf16(void* stream, const void* proj, int width, in
     p.eps = eps;
     p.per_head = norm_scope == FV_NORM_PER_HEAD;
     const int threads = (heads * 16 + 31) & ~31;
-    const char* which = getenv("FV_PREP_KERNEL");  // "row": the one-CTA-per-row kernel (A/B timing)
-    if (!(which && which[0] == 'r')) {
-        // ring geometry: stage = q | k | v | cos | sin; as many stages as fit, several CTAs per SM for narrow rows
-        const uint32_t dimB = (uint32_t)dim * 2u;
-        fvprep::RingGeom g{};
-        g.off_k = dimB;
-        g.off_v = 2 * dimB;
-        g.off_cos = 3 * dimB;
-        g.off_sin = 3 * dimB + 512;
-        g.stage_bytes = 3 * dimB + 1024;
-        g.rows = (long long)batch * seq;
-        rc = fvrt::status_word(dev, &g.status);
-        if (rc != FV_RAN) return rc;
-        const int ctas_per_sm = threads <= 256 ? 4 : (threads <= 320 ? 2 : 1);
-        const uint32_t budget = (200u / (uint32_t)ctas_per_sm) * 1024u;
-        g.stages = (int)(budget / g.stage_bytes);
-        if (g.stages > 8) g.stages = 8;
-        if (g.stages < 2) g.stages = 2;
-        const size_t extra = 8 * (size_t)g.stages + 16 * (size_t)(threads / 32) + 16;
-        const size_t smem_ring = (size_t)g.stages * g.stage_bytes + extra;
+    const char* which = getenv("FV_PREP_KERNEL");  // "row": the one-CTA-per-row kernel (A/B timing and the bit-equality test)
+    if (!which || which[0] != 'r') {
         int sms = 0;
-        FV_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        long long grid = (long long)sms * ctas_per_sm;
-        if (grid > g.rows) grid = g.rows;
-        auto run = [&](auto kern) -> int {
-            FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_ring));
-            kern<<<(unsigned)grid, threads, smem_ring, (cudaStream_t)stream>>>(p, g);
-            FV_CUDA(cudaGetLastError());
-            return FV_RAN;
-        };
-        if (threads <= 256) return run(fvprep::fv_wan_qk_prep_ring_kernel<256, 4>);
-        if (threads <= 640) return run(fvprep::fv_wan_qk_prep_ring_kernel<640, 1>);
-        return run(fvprep::fv_wan_qk_prep_ring_kernel<1024, 1>);
+        rc = fvrt::sm_count(dev, &sms);
+        if (rc != FV_RAN) return rc;
+        const long long rows = (long long)batch * seq;
+        const int chunks = heads * 16;
+        // warps per row: 8 above 40 heads, 4 above 16, 2 above 8, else 1; chunks per thread follow (at most 5)
+        const int G = heads > 40 ? 8 : (heads > 16 ? 4 : (heads > 8 ? 2 : 1));
+        if (G == 8) rc = fvprep::launch_group<8, 1>(p, rows, (chunks + 255) / 256, sms, (cudaStream_t)stream);
+        else if (G == 4) rc = fvprep::launch_group<4, 2>(p, rows, (chunks + 127) / 128, sms, (cudaStream_t)stream);
+        else if (G == 2) rc = fvprep::launch_group<2, 4>(p, rows, (chunks + 63) / 64, sms, (cudaStream_t)stream);
+        else rc = fvprep::launch_group<1, 8>(p, rows, (chunks + 31) / 32, sms, (cudaStream_t)stream);
+        if (rc == FV_RAN)
+            fvrt::ran(fvrt::kLogPrep, "qk_prep: fv_wan_qk_prep_group_kernel (%d warps per row, rows in registers) %lld rows x %d heads", G, rows, heads);
+        return rc;
     }
     const size_t smem = 2 * (threads / 32 + 1) * sizeof(float);
     // up to 40 heads: 640-thread blocks, two per SM (register cap 51); beyond: one block of up to 1024 threads

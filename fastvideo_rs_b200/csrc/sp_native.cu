@@ -81,6 +81,7 @@ static int load_nccl() {
 
 struct Sp {
     int world = 1, rank = 0, seq = 0, bh = 0, groups = 1, bh_g = 0, dev = 0;
+    double op_timeout_s = 120.0;  // how long settle() polls a call the non-blocking communicator left in progress
     int start = 0, len = 0, seg_rows = 0;
     std::vector<int> starts, lens;
     void* comm = nullptr;
@@ -94,6 +95,27 @@ struct Sp {
     float* o1 = nullptr;    // [bh, len, 128]
     float* lse1 = nullptr;  // [bh, len]
 };
+
+// A communicator formed in non-blocking mode (the rendezvous with a deadline) answers ncclInProgress (7) from
+// any call; the call has completed on the host side once ncclCommGetAsyncError stops saying so, and nothing
+// else may be issued on the communicator before that.  Returns the settled NCCL result.
+constexpr int kNcclInProgress = 7;
+static int settle(Sp* s, int nrc) {
+    if (nrc != kNcclInProgress || !g_nccl.CommGetAsyncError) return nrc;
+    timespec t0;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (;;) {
+        int state = 0;
+        const int q = g_nccl.CommGetAsyncError(s->comm, &state);
+        if (q != 0) return q;
+        if (state != kNcclInProgress) return state;
+        timespec t1;
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        if ((double)(t1.tv_sec - t0.tv_sec) + 1e-9 * (double)(t1.tv_nsec - t0.tv_nsec) > s->op_timeout_s) return kNcclInProgress;
+        const timespec nap = {0, 20000};
+        nanosleep(&nap, nullptr);
+    }
+}
 
 static void release(Sp* s) {
     if (!s) return;
@@ -166,10 +188,10 @@ static int forward(Sp* s, cudaStream_t stream, const void* q, const void* k, con
     FV_CUDA(cudaStreamWaitEvent(s->comm_stream, s->ready, 0));
     const size_t group_elems = (size_t)s->bh_g * s->seg_rows * kD;
     for (int g = 0; g < s->groups; g++) {
-        FV_NCCL(g_nccl.AllGather(static_cast<const __nv_bfloat16*>(ks) + g * group_elems, s->k_all[g], group_elems, kNcclBf16,
-                                 s->comm, s->comm_stream));
-        FV_NCCL(g_nccl.AllGather(static_cast<const __nv_bfloat16*>(vs) + g * group_elems, s->v_all[g], group_elems, kNcclBf16,
-                                 s->comm, s->comm_stream));
+        FV_NCCL(settle(s, g_nccl.AllGather(static_cast<const __nv_bfloat16*>(ks) + g * group_elems, s->k_all[g], group_elems, kNcclBf16,
+                                           s->comm, s->comm_stream)));
+        FV_NCCL(settle(s, g_nccl.AllGather(static_cast<const __nv_bfloat16*>(vs) + g * group_elems, s->v_all[g], group_elems, kNcclBf16,
+                                           s->comm, s->comm_stream)));
         FV_CUDA(cudaEventRecord(s->arrived[g], s->comm_stream));
     }
     if (s->len == 0) {  // more ranks than tokens: this rank only takes part in the exchange
@@ -330,6 +352,7 @@ static int create(const void* unique_id, int world, int rank, int seq, int bh, i
     memcpy(id.bytes, unique_id, sizeof(id.bytes));
     rc = init_comm(s, id, world, rank, timeout_s);
     if (rc != FV_RAN) return bail(rc);
+    if (timeout_s > 0) s->op_timeout_s = timeout_s;
     // Every rank must describe the same problem: a rank with another seq, bh or group count would size its
     // gathers differently and the first exchange would never complete.  One small all-gather settles it here,
     // where a mismatch is an error return on every rank instead of a hang later.
@@ -340,7 +363,7 @@ static int create(const void* unique_id, int world, int rank, int seq, int bh, i
         cudaError_t e = cudaMalloc(&shape_dev, sizeof(int) * 4 * ((size_t)world + 1));
         if (e == cudaSuccess) e = cudaMemcpy(shape_dev + 4 * (size_t)world, mine, sizeof(mine), cudaMemcpyHostToDevice);
         int nrc = 0;
-        if (e == cudaSuccess) nrc = g_nccl.AllGather(shape_dev + 4 * (size_t)world, shape_dev, 16, /* ncclInt8 */ 0, s->comm, s->comm_stream);
+        if (e == cudaSuccess) nrc = settle(s, g_nccl.AllGather(shape_dev + 4 * (size_t)world, shape_dev, 16, /* ncclInt8 */ 0, s->comm, s->comm_stream));
         if (e == cudaSuccess && nrc == 0) e = cudaStreamSynchronize(s->comm_stream);
         if (e == cudaSuccess && nrc == 0) e = cudaMemcpy(all.data(), shape_dev, sizeof(int) * 4 * (size_t)world, cudaMemcpyDeviceToHost);
         if (shape_dev) cudaFree(shape_dev);

@@ -67,7 +67,7 @@ struct Geo {
 
 // MODE 0: ln_adaln_e.  MODE 1: self_residual_norm.
 template <int G, int MODE>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, MODE == 0 ? 3 : 2)
 fv_wan_glue_kernel(const uint4* __restrict__ x, const uint4* __restrict__ a, const float* __restrict__ e, int slot0, int slot1,
                    const float* __restrict__ w, const float* __restrict__ b, uint4* __restrict__ out0, uint4* __restrict__ out1,
                    Geo g, float eps) {
@@ -77,29 +77,62 @@ fv_wan_glue_kernel(const uint4* __restrict__ x, const uint4* __restrict__ a, con
     const int sub = warp % G;  // this warp's part of the row
     const float inv_dim = 1.0f / (float)g.dim;
     int it = 0;
-    for (long row0 = (long)blockIdx.x * rows_per_cta; row0 < g.rows; row0 += (long)gridDim.x * rows_per_cta, it++) {
+    const long stride = (long)gridDim.x * rows_per_cta;
+    // The x vectors of a row (MODE 0: requested one row ahead, so that a row's loads are in flight while the
+    // row before it goes through its two reductions; MODE 1 has twice the loads per row and does without).
+    auto load_x = [&](long row0, uint4 (&dst)[kVec]) -> int {
+        const long row = row0 + warp / G;
+        int n = 0;
+        if (row < g.rows) {
+            const long base = row * (long)g.nvec;
+#pragma unroll
+            for (int i = 0; i < kVec; i++) {
+                const int vec = (i * G + sub) * 32 + lane;
+                if (vec < g.nvec) {
+                    dst[i] = x[base + vec];
+                    n = i + 1;
+                }
+            }
+        }
+        return n;
+    };
+    uint4 xr[kVec], nx[kVec];
+    int cnt = 0, ncnt = 0;
+    if (MODE == 0 && (long)blockIdx.x * rows_per_cta < g.rows) ncnt = load_x((long)blockIdx.x * rows_per_cta, nx);
+    for (long row0 = (long)blockIdx.x * rows_per_cta; row0 < g.rows; row0 += stride, it++) {
         const long row = row0 + warp / G;
         const bool live = row < g.rows;  // (a dead warp still takes part in the CTA's barriers)
         const long base = (live ? row : 0) * (long)g.nvec;
         const long tb = (live ? row / g.seq : 0) * (long)g.e_rows;
-        float v[kVec][8];
-        int cnt = 0;
-        // every load of the row first
-        uint4 xr[kVec], ar[kVec];
+        float v[MODE == 0 ? 1 : kVec][8];  // MODE 1 keeps the unrounded sums; MODE 0 unpacks xr again in every pass
+        uint4 ar[kVec];
+        auto vals = [&](int i, float (&f)[8]) {
+            if (MODE == 0) {
+                unpack8(xr[i], f);
+            } else {
 #pragma unroll
-        for (int i = 0; i < kVec; i++) {
-            const int vec = (i * G + sub) * 32 + lane;
-            if (vec < g.nvec && live) {
-                xr[i] = x[base + vec];
-                if (MODE == 1) ar[i] = a[base + vec];
-                cnt = i + 1;
+                for (int c = 0; c < 8; c++) f[c] = v[MODE == 0 ? 0 : i][c];
+            }
+        };
+        if (MODE == 0) {
+            cnt = ncnt;
+#pragma unroll
+            for (int i = 0; i < kVec; i++) xr[i] = nx[i];
+            ncnt = row0 + stride < g.rows ? load_x(row0 + stride, nx) : 0;
+        } else {
+            cnt = load_x(row0, xr);
+#pragma unroll
+            for (int i = 0; i < kVec; i++) {
+                const int vec = (i * G + sub) * 32 + lane;
+                if (i < cnt) ar[i] = a[base + vec];
             }
         }
         float s = 0.f;
 #pragma unroll
         for (int i = 0; i < kVec; i++) {
             if (i < cnt) {
-                unpack8(xr[i], v[i]);
+                float f[8];
+                unpack8(xr[i], f);
                 if (MODE == 1) {
                     const int vec = (i * G + sub) * 32 + lane;
                     float av[8];
@@ -108,11 +141,11 @@ fv_wan_glue_kernel(const uint4* __restrict__ x, const uint4* __restrict__ a, con
                     const float4 g0 = gp[0], g1 = gp[1];
                     const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
-                    for (int c = 0; c < 8; c++) v[i][c] = __fadd_rn(v[i][c], __fmul_rn(av[c], gg[c]));
-                    out0[base + vec] = pack8(v[i]);  // the new hidden state, rounded
+                    for (int c = 0; c < 8; c++) f[c] = v[MODE == 0 ? 0 : i][c] = __fadd_rn(f[c], __fmul_rn(av[c], gg[c]));
+                    out0[base + vec] = pack8(f);  // the new hidden state, rounded
                 }
 #pragma unroll
-                for (int c = 0; c < 8; c++) s += v[i][c];
+                for (int c = 0; c < 8; c++) s += f[c];
             }
         }
         const float mean = group_sum<G>(s, red[(it & 1) * 2], warp) * inv_dim;
@@ -120,9 +153,11 @@ fv_wan_glue_kernel(const uint4* __restrict__ x, const uint4* __restrict__ a, con
 #pragma unroll
         for (int i = 0; i < kVec; i++) {
             if (i < cnt) {
+                float f[8];
+                vals(i, f);
 #pragma unroll
                 for (int c = 0; c < 8; c++) {
-                    const float d = v[i][c] - mean;
+                    const float d = f[c] - mean;
                     q = fmaf(d, d, q);
                 }
             }
@@ -132,7 +167,8 @@ fv_wan_glue_kernel(const uint4* __restrict__ x, const uint4* __restrict__ a, con
         for (int i = 0; i < kVec; i++) {
             if (i < cnt) {
                 const int vec = (i * G + sub) * 32 + lane;
-                float y[8];
+                float y[8], f[8];
+                vals(i, f);
                 if (MODE == 0) {
                     const float4* sp = reinterpret_cast<const float4*>(e + (tb + slot0) * (long)g.dim + (long)vec * 8);
                     const float4* hp = reinterpret_cast<const float4*>(e + (tb + slot1) * (long)g.dim + (long)vec * 8);
@@ -140,7 +176,7 @@ fv_wan_glue_kernel(const uint4* __restrict__ x, const uint4* __restrict__ a, con
                     const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
                     const float sh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
-                    for (int c = 0; c < 8; c++) y[c] = ((v[i][c] - mean) * inv) * (1.0f + sc[c]) + sh[c];
+                    for (int c = 0; c < 8; c++) y[c] = ((f[c] - mean) * inv) * (1.0f + sc[c]) + sh[c];
                     out0[base + vec] = pack8(y);
                 } else {
                     const float4* wp = reinterpret_cast<const float4*>(w + (long)vec * 8);
@@ -150,7 +186,7 @@ fv_wan_glue_kernel(const uint4* __restrict__ x, const uint4* __restrict__ a, con
                     const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
                     for (int c = 0; c < 8; c++)
-                        y[c] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v[i][c], mean), inv), ww[c]), bb[c]);
+                        y[c] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(f[c], mean), inv), ww[c]), bb[c]);
                     out1[base + vec] = pack8(y);
                 }
             }

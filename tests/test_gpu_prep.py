@@ -41,11 +41,12 @@ def test_prep_matches_oracle(fvlib, oracle, batch, grid, heads, per_head):
 
 @pytest.mark.parametrize("batch,grid,heads,per_head", [(1, (3, 40, 50), 12, False), (2, (2, 30, 40), 40, False),
                                                        (1, (3, 30, 40), 20, False), (1, (3, 20, 25), 48, False),
-                                                       (1, (3, 40, 50), 12, True), (1, (5, 40, 50), 1, False)])
-def test_prep_ring_turns_over_and_equals_the_row_kernel(fvlib, oracle, batch, grid, heads, per_head, monkeypatch):
-    """Enough rows that every persistent CTA refills its ring several times (each launch configuration of the
-    staged kernel: 4, 2 and 1 CTAs per SM, 640- and 1024-thread blocks): equal to the oracle on sampled rows,
-    and bit for bit to the one-CTA-per-row kernel everywhere."""
+                                                       (1, (3, 40, 50), 12, True), (1, (5, 40, 50), 1, False), (1, (3, 20, 25), 64, False),
+                                                       (1, (3, 20, 25), 7, False), (2, (3, 20, 25), 16, True), (1, (2, 20, 25), 33, False)])
+def test_prep_group_kernel_equals_the_row_kernel(fvlib, oracle, batch, grid, heads, per_head, monkeypatch):
+    """Enough rows that every persistent group of warps walks several rows, in each launch configuration of the
+    default kernel (1, 2, 4 and 8 warps per row; 1 to 5 chunks per thread, ragged last chunk): equal to the oracle
+    on sampled rows, and bit for bit to the one-CTA-per-row kernel everywhere (same reduction tree)."""
     from fastvideo_rs_b200 import wan
     seq = grid[0] * grid[1] * grid[2]
     dim = heads * 128
@@ -92,3 +93,31 @@ def test_prep_rejects_bad_columns(fvlib, oracle):
     w = torch.ones(1536, device="cuda")
     with pytest.raises(FvError):
         wan.qk_prep(proj, w, w, None, None, 12)  # k and v columns fall outside a width-1536 row
+
+
+def test_prep_slab_of_wan14b_rows(fvlib, oracle):
+    """7 200 token rows of the Wan-14B width (40 heads, 30 KB per row in, 30 KB out: past L2 in both directions),
+    the case the profile of the default kernel is captured on: V bit-exact, q and k against the oracle on sampled
+    tokens."""
+    from fastvideo_rs_b200 import sdpa, wan
+    batch, grid, heads = 1, (2, 45, 80), 40
+    seq, dim = grid[0] * grid[1] * grid[2], heads * 128
+    proj = oracle.bf16_round(oracle.seeded_normal(34, 0, (batch, seq, 3 * dim)))
+    w = (1.0 + 0.1 * oracle.seeded_normal(34, 1, (dim,))).astype(np.float32)
+    tc, ts = wan.wan_rope_tables(grid)
+    tw = torch.from_numpy(w).cuda()
+    q, k, v = wan.qk_prep(to_dev_bf16(proj), tw, tw, tc, ts, heads)
+    assert sdpa.device_status() == 0
+    assert "group_kernel" in sdpa._lib.last_kernel()
+    tok = np.unique(np.concatenate([[0, 1, seq - 1], np.random.default_rng(5).integers(0, seq, 61)]))
+    cos, sin = oracle.wan_rope(*grid)
+    sub = np.ascontiguousarray(proj[:, tok])
+    want_q = oracle.qk_norm_rope_bhsd(sub, w, cos[tok], sin[tok], batch, len(tok), heads, 128, 3 * dim, 0)
+    want_k = oracle.qk_norm_rope_bhsd(sub, w, cos[tok], sin[tok], batch, len(tok), heads, 128, 3 * dim, dim)
+    want_v = oracle.split_heads_bhsd(sub, batch, len(tok), heads, 128, 3 * dim, 2 * dim)
+    tt = torch.from_numpy(tok).cuda()
+    assert np.array_equal(to_host_f32(v[:, :, tt]).reshape(heads, len(tok), 128), want_v)
+    for got, want in ((q, want_q), (k, want_k)):
+        g = to_host_f32(got[:, :, tt]).reshape(heads, len(tok), 128)
+        assert np.mean(g != oracle.bf16_round(want)) < 2e-3
+        assert np.abs(g - want).max() <= np.abs(want).max() * 2.0 ** -8
