@@ -56,7 +56,7 @@ WORKLOADS = {
     "wan1p3b_ar_kvwindow": dict(batch=1, heads=12, grid=(3, 30, 52), block=0, window=32760, rope_grid=(21, 30, 52),
                                 desc="causal (Self-Forcing) Wan-1.3B inference step: one block of 3 latent frames (4 680 rows) "
                                      "against the cached 21-frame window (32 760 keys), Plan.kv_window; the step is prologue of the "
-                                     "block + write of its k/v into the cache tail + attention (keys cut in ranges when that fills "
+                                     "block, which writes its k/v into the cache tail, + attention (keys cut in ranges when that fills "
                                      "the SMs better; FV_SPLITKV=0 turns that off)"),
     "tiny": dict(batch=1, heads=12, grid=(3, 8, 8), block=0, desc="tiny Wan-arch dense self-attention (192 tokens)"),
 }
@@ -147,7 +147,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "25",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
             self.t.start()
@@ -327,9 +327,13 @@ class Bench:
                 self.attn_events.append((e0, e1))
             return o
         n = self.length
-        q, k, v = self.wan.qk_prep(p, self.wq, self.wk, self.cos, self.sin, self.heads, want_k=not self.cross, want_v=not self.cross)
+        if self.window:  # the block's K and V go straight into the cache tail (no copy launches)
+            q, k, v = self.wan.qk_prep(p, self.wq, self.wk, self.cos, self.sin, self.heads,
+                                       cache=(self.k_cache, self.v_cache, self.window - self.seq))
+        else:
+            q, k, v = self.wan.qk_prep(p, self.wq, self.wk, self.cos, self.sin, self.heads, want_k=not self.cross, want_v=not self.cross)
         q = q.view(self.bh, n, 128)
-        if not self.cross:
+        if not self.cross and not self.window:
             k, v = k.view(self.bh, n, 128), v.view(self.bh, n, 128)
         if keep:
             self.last_qkv = (q, k, v)
@@ -337,8 +341,6 @@ class Bench:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
         if self.window:
-            self.k_cache[:, :, self.window - self.seq:].copy_(k.view(self.batch, self.heads, self.seq, 128))
-            self.v_cache[:, :, self.window - self.seq:].copy_(v.view(self.batch, self.heads, self.seq, 128))
             o = self.sdpa.sdpa(q.view(self.batch, self.heads, self.seq, 128), self.k_cache, self.v_cache,
                                self.sdpa.Plan.kv_window()).view(self.bh, self.seq, 128)
         elif self.cross:
@@ -523,7 +525,7 @@ def roofline_of(b: Bench, attn_ms, pk):
     rank_flops = b.flops / b.world
     achieved = rank_flops / (attn_ms * 1e-3) / 1e12
     kernel = "fv_vsa_fine_kernel (+4 small kernels in the timed span)" if b.vsa_topk else \
-        ("fv_attn_fwd_d128 (+ cache-tail copies and fv_splitkv_merge_kernel in the timed span)" if b.window else "fv_attn_fwd_d128")
+        ("fv_attn_fwd_d128 (+ fv_splitkv_merge_kernel in the timed span)" if b.window else "fv_attn_fwd_d128")
     # DRAM bytes per attention launch: measured on a smaller case of the same kernel (ncu dram__bytes_read.sum +
     # dram__bytes_write.sum of a 24-head x 8192-token capture: reads = 1.0007 x (Q + K + V), every output byte written
     # once) and scaled by the bytes of Q, K, V and O, which is what the traffic is proportional to.

@@ -51,11 +51,16 @@
 //                   warps share one MUFU pipe per scheduler (4 results per cycle), which at 128 x 128
 //                   exponentials per tile is exactly as long as the tile's two MMAs: moving a share of them
 //                   to the FMA pipe, evenly interleaved, is what lets the two overlap.
+//   FV_ATT_EARLY    keys of a tile whose P is handed to the issuer first (64 or 96), the rest follows; 128: P is
+//                   handed over whole (one wait and no pv_early commit per tile for the issuer)
 //   FV_ATT_SPLIT    TMEM map: 1 = S_A S_B O_A O_B, 0 = S_A O_A S_B O_B (no measurable difference)
 //   FV_ATT_BACKOFF  nanoseconds a waiting softmax thread sleeps between two probes of its barrier (0 = none);
 //                   FV_ATT_BACKOFF_LOADER the same for the loader thread
 #ifndef FV_ATT_POLY
-#define FV_ATT_POLY 0
+#define FV_ATT_POLY 4
+#endif
+#ifndef FV_ATT_EARLY
+#define FV_ATT_EARLY 128
 #endif
 #ifndef FV_ATT_SPLIT
 #define FV_ATT_SPLIT 1
@@ -81,12 +86,16 @@ constexpr int kSoftmaxWarps = 8;
 constexpr int kLoaderWarp = 8;
 constexpr int kIssuerWarp = 9;
 constexpr int kQSlots = 3;
-constexpr int kKvSlots = 4;
+constexpr int kKvSlots = 4;     // 32 KB tiles; they are filled and freed in PAIRS [V(j-1) | K(j)]: one barrier each way per step
+constexpr int kKvPairs = kKvSlots / 2;
 constexpr uint32_t kSlotBytes = 32768;   // 128 rows x 128 bf16: two 64-column swizzled panels
 constexpr uint32_t kPanelBytes = 16384;
 constexpr int kMaxSeg = 16;
 constexpr float kGuard = 1099511627776.f;  // 2^40: a row sum of P above this sends the tile down the exact path
 constexpr uint32_t kFullWarp = 0xffffffffu;
+constexpr int kEarlyKeys = FV_ATT_EARLY;       // P of keys [0, kEarlyKeys) is stored and signalled first (p_early)
+constexpr int kEarlyChunks = kEarlyKeys / 32;  // in 32-column chunks of S
+static_assert(kEarlyKeys == 64 || kEarlyKeys == 96 || kEarlyKeys == 128, "FV_ATT_EARLY is 64, 96 or 128 (128: P handed over whole)");
 
 // Shared-memory map, offsets from the (1024-byte aligned) start of dynamic shared memory.
 struct Smem {
@@ -95,14 +104,14 @@ struct Smem {
     static constexpr uint32_t q_full = kv + kKvSlots * kSlotBytes;  // mbarriers, 8 bytes each
     static constexpr uint32_t q_free = q_full + 8 * kQSlots;
     static constexpr uint32_t kv_full = q_free + 8 * kQSlots;
-    static constexpr uint32_t kv_free = kv_full + 8 * kKvSlots;
+    static constexpr uint32_t kv_free = kv_full + 8 * kKvSlots;  // (kKvPairs of each are used)
     static constexpr uint32_t s_ready = kv_free + 8 * kKvSlots;  // [2] S_t complete (issuer -> softmax)
-    static constexpr uint32_t p_early = s_ready + 16;            // [2] keys 0-63 of P_t stored (softmax -> issuer)
+    static constexpr uint32_t p_early = s_ready + 16;            // [2] the early keys of P_t stored (softmax -> issuer)
     static constexpr uint32_t p_ready = p_early + 16;            // [2] all of P_t stored
-    static constexpr uint32_t pv_early = p_ready + 16;           // [2] the product over keys 0-63 has run (issuer -> softmax)
+    static constexpr uint32_t pv_early = p_ready + 16;           // [2] the product over the early keys has run (issuer -> softmax)
     static constexpr uint32_t o_ready = pv_early + 16;           // [2] O_t of the item complete
-    static constexpr uint32_t drain = o_ready + 16;
-    static constexpr uint32_t tmem_slot = drain + 8;
+    static constexpr uint32_t drain = o_ready + 16;              // [2] everything an issuer thread issued has completed
+    static constexpr uint32_t tmem_slot = drain + 16;
     static constexpr uint32_t abort_flag = tmem_slot + 4;
     static constexpr uint32_t total = abort_flag + 4;
 };
@@ -291,7 +300,7 @@ FV_DEV void scores_mma(uint32_t tS, uint64_t qd, uint64_t kd) {
 // O (128 x 128 f32, TMEM) (+)= P . V.  P comes from TMEM: key slice s (16 keys) at column 8 s of the
 // row tile's score block.  V is MN-major in shared memory (64-column
 // panels 16 KB apart, 8-key groups 1024 bytes apart): slice s starts 2 KB = 128 address units further.
-// Two statements of four slices: keys 0-63 (the first slice overwrites O when `fresh`) and keys 64-127.
+// Two statements: keys [0, kEarlyKeys) (the first slice overwrites O when `fresh`) and the rest.
 FV_DEV void output_mma_early(uint32_t tO, uint32_t tP, uint64_t vd, bool fresh) {
     constexpr uint32_t idesc = umma_idesc_bf16(kRowTile, kD, 1);
     asm volatile(
@@ -299,16 +308,26 @@ FV_DEV void output_mma_early(uint32_t tO, uint32_t tP, uint64_t vd, bool fresh) 
         "setp.eq.b32 p0, %4, 0;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
         FV_PV_STEP(8, 128) FV_PV_STEP(16, 256) FV_PV_STEP(24, 384)
+#if FV_ATT_EARLY >= 96
+        FV_PV_STEP(32, 512) FV_PV_STEP(40, 640)
+#endif
+#if FV_ATT_EARLY == 128
+        FV_PV_STEP(48, 768) FV_PV_STEP(56, 896)
+#endif
         "}"
         ::"r"(tO), "r"(tP), "l"(vd), "r"(idesc), "r"(fresh ? 1u : 0u)
         : "memory");
 }
 FV_DEV void output_mma_late(uint32_t tO, uint32_t tP, uint64_t vd) {
     constexpr uint32_t idesc = umma_idesc_bf16(kRowTile, kD, 1);
+    if (kEarlyKeys == 128) return;
     asm volatile(
         "{\n\t.reg .pred pt;\n\t.reg .b64 b;\n\t.reg .b32 t;\n\t"
         "setp.eq.b32 pt, %3, %3;\n\t"
-        FV_PV_STEP(32, 512) FV_PV_STEP(40, 640) FV_PV_STEP(48, 768) FV_PV_STEP(56, 896)
+#if FV_ATT_EARLY == 64
+        FV_PV_STEP(32, 512) FV_PV_STEP(40, 640)
+#endif
+        FV_PV_STEP(48, 768) FV_PV_STEP(56, 896)
         "}"
         ::"r"(tO), "r"(tP), "l"(vd), "r"(idesc)
         : "memory");
@@ -403,48 +422,48 @@ FV_DEV float max32(const uint32_t (&u)[32]) {
 struct Cols {
     int lo, hi, sink;
     bool whole;  // every one of the 128 columns is visible
-    template <int C0>
-    FV_DEV void hide(uint32_t (&x)[32]) const {  // columns C0 .. C0 + 31: the invisible ones become -inf
+    FV_DEV void hide(uint32_t (&x)[32], int c0) const {  // columns c0 .. c0 + 31: the invisible ones become -inf
         if (whole) return;
 #pragma unroll
         for (int c = 0; c < 32; c++) {
-            const bool vis = (C0 + c >= lo && C0 + c < hi) || C0 + c < sink;
+            const bool vis = (c0 + c >= lo && c0 + c < hi) || c0 + c < sink;
             x[c] = vis ? x[c] : as_u(neg_inf());
         }
     }
 };
 
-// Exponentials of one half (64 columns) of this thread's row of S out of two 32-column register arrays
-// whose TMEM loads have completed: P = 2^(s * sl2 + noff) as 32 packed words, returns the half row's sum.
+// Sum of the four lanes of two packed accumulators; with POLY an argument the polynomial cannot take makes
+// the sum infinite, so that the caller's guard sends the tile the careful way.
 template <bool POLY>
-FV_DEV float half_exp(const uint32_t (&ua)[32], const uint32_t (&ub)[32], float sl2, float noff, uint32_t (&pw)[32]) {
-    uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
-    const uint64_t s2 = pack_f32x2(sl2, sl2), nf = pack_f32x2(noff, noff);
-    float top = 0.f;
-    exp32<POLY>(ua, pw, s2, nf, acc0, acc1, top);
-    exp32<POLY>(ub, pw + 16, s2, nf, acc0, acc1, top);
+FV_DEV float part_sum(uint64_t acc0, uint64_t acc1, float top) {
     float a, b, c, d;
     unpack_f32x2(acc0, a, b);
     unpack_f32x2(acc1, c, d);
     const float sum = (a + b) + (c + d);
-    // (an argument the polynomial cannot take makes the half row's sum infinite: the guard sends the tile the careful way)
     return (POLY && top > 120.f) ? __int_as_float(0x7f800000) : sum;
 }
-FV_DEV void load_half(uint32_t tS_half, uint32_t (&ua)[32], uint32_t (&ub)[32]) {
-    tmem_ld32_issue(tS_half, ua);
-    tmem_ld32_issue(tS_half + 32u, ub);
-}
-FV_DEV void land_half(uint32_t (&ua)[32], uint32_t (&ub)[32]) {
+// One 32-column chunk of this thread's row of S: issue, and "landed" (every chunk issued so far is in registers).
+FV_DEV void load_chunk(uint32_t tS, int chunk, uint32_t (&u)[32]) { tmem_ld32_issue(tS + 32u * (uint32_t)chunk, u); }
+FV_DEV void land_chunk(uint32_t (&u)[32]) {
     tmem_ld_wait();
-    tmem_pin(ua);
-    tmem_pin(ub);
+    tmem_pin(u);
 }
-// P of 64 keys into TMEM at column `col` of the row's score block, then the warp's arrival at `bar`.
-FV_DEV void hand_over(uint32_t tS, uint32_t col, const uint32_t (&pw)[32], uint32_t bar, int lane) {
-    tmem_st32(tS + col, pw);
+// The stores of P issued so far are complete and ordered before the arrival that publishes them.
+FV_DEV void publish(uint32_t bar, int lane) {
     tmem_st_wait();
     tc_fence_before();
     warp_arrive(bar, lane);
+}
+// P words of the early part (keys [0, kEarlyKeys): 16 kEarlyChunks words from column 0 of the score block) and
+// of the late part, out of one 64-word array.
+FV_DEV void store_early(uint32_t tS, const uint32_t (&pw)[64]) {
+    tmem_st32_at<0>(tS, pw);
+    if (kEarlyChunks == 3) tmem_st16_at<32>(tS + 32u, pw);
+    if (kEarlyChunks == 4) tmem_st32_at<32>(tS + 32u, pw);
+}
+FV_DEV void store_late(uint32_t tS, const uint32_t (&pw)[64]) {
+    if (kEarlyChunks == 3) tmem_st16_at<48>(tS + 48u, pw);
+    else tmem_st32_at<32>(tS + 32u, pw);
 }
 
 // What a row carries from key tile to key tile.
@@ -452,32 +471,28 @@ struct RowState {
     float m, l;  // reference (base-2 domain, -inf = none yet) and sum of P against it
 };
 
-// The careful way through one key tile (or through its second half): masks honoured, exact row maxima
+// The careful way through one key tile (or through its late part): masks honoured, exact row maxima
 // first, the reference moved where it is missing or more than 2^8 behind, O and the row sum brought
 // to the new reference, P evaluated on the MUFU path (an invisible column gives an exact zero).  Kept
 // OUT OF LINE on purpose: it runs on the first tile of an item, on tiles a mask cuts through, on a
 // segment's last partial tile and when a guard trips, and inlined it more than doubled the code the
 // hot loop is spread over (instruction-fetch stalls tripled).
-//   second_only: the first half of P is already with the issuer (stored against the old reference);
+//   late_only: the early part of P is already with the issuer (stored against the old reference);
 //   its product must have finished before O is touched -- the caller has waited for pv_early.
-//   have_o: O holds products of this item (earlier tiles, or this tile's first half).
-__device__ __noinline__ void careful_tile(uint32_t tS, uint32_t tO, uint32_t bt, Cols cols, float sl2, bool second_only,
+//   have_o: O holds products of this item (earlier tiles, or this tile's early part).
+__device__ __noinline__ void careful_tile(uint32_t tS, uint32_t tO, uint32_t bt, Cols cols, float sl2, bool late_only,
                                           bool have_o, int lane, RowState* rs) {
     float m = rs->m, l = rs->l;
-    uint32_t ua[32], ub[32];
+    const int first = late_only ? kEarlyChunks : 0;
     float mx = neg_inf();
-    if (!second_only) {
-        load_half(tS, ua, ub);
-        land_half(ua, ub);
-        cols.hide<0>(ua);
-        cols.hide<32>(ub);
-        mx = fmaxf(max32(ua), max32(ub));
+#pragma unroll 1
+    for (int c = first; c < 4; c++) {
+        uint32_t u[32];
+        load_chunk(tS, c, u);
+        land_chunk(u);
+        cols.hide(u, 32 * c);
+        mx = fmaxf(mx, max32(u));
     }
-    load_half(tS + 64u, ua, ub);
-    land_half(ua, ub);
-    cols.hide<64>(ua);
-    cols.hide<96>(ub);
-    mx = fmaxf(mx, fmaxf(max32(ua), max32(ub)));
     const float cand = mx * sl2;
     float a = 1.f;
     if (cand > m + 8.f) {   // (-inf + 8 = -inf: any finite maximum replaces a missing reference)
@@ -498,18 +513,22 @@ __device__ __noinline__ void careful_tile(uint32_t tS, uint32_t tO, uint32_t bt,
         }
     }
     const float noff = (m == neg_inf()) ? 0.f : -m;  // a row that still sees nothing: P = 2^-inf = 0
-    uint32_t pw[32];
-    if (!second_only) {
-        uint32_t uc[32], ud[32];
-        load_half(tS, uc, ud);
-        land_half(uc, ud);
-        cols.hide<0>(uc);
-        cols.hide<32>(ud);
-        l += half_exp<false>(uc, ud, sl2, noff, pw);
-        hand_over(tS, 0u, pw, bt + Smem::p_early, lane);
+    const uint64_t s2 = pack_f32x2(sl2, sl2), nf = pack_f32x2(noff, noff);
+    // Chunk by chunk: P of chunk c (16 words at column 16 c) only overwrites scores that have been read.
+#pragma unroll 1
+    for (int c = first; c < 4; c++) {
+        uint32_t u[32], pw[16];
+        load_chunk(tS, c, u);
+        land_chunk(u);
+        cols.hide(u, 32 * c);
+        uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
+        float top = 0.f;
+        exp32<false>(u, pw, s2, nf, acc0, acc1, top);
+        l += part_sum<false>(acc0, acc1, top);
+        tmem_st16(tS + 16u * (uint32_t)c, pw);
+        if (kEarlyChunks < 4 && c == kEarlyChunks - 1) publish(bt + Smem::p_early, lane);
     }
-    l += half_exp<false>(ua, ub, sl2, noff, pw);  // (ua, ub still hold the masked scores of the second half)
-    hand_over(tS, 32u, pw, bt + Smem::p_ready, lane);
+    publish(bt + Smem::p_ready, lane);
     rs->m = m;
     rs->l = l;
 }
@@ -584,33 +603,59 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
             // everything below is warp-collective); the rest goes the careful way.
             bool hot = seen > 0 && __all_sync(kFullWarp, cols.whole && rs.m != neg_inf());
             if (hot) {
-                uint32_t ua[32], ub[32], pw[32];
-                load_half(tS, ua, ub);
-                land_half(ua, ub);
+                // Four 32-column chunks, the next one on its way from TMEM while this one's exponentials run.
+                uint32_t u0[32], u1[32], pw[64];
+                const uint64_t s2 = pack_f32x2(sl2, sl2), nf = pack_f32x2(-rs.m, -rs.m);
+                uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
+                float top = 0.f;
+                load_chunk(tS, 0, u0);
+                land_chunk(u0);
                 if (tr) FV_TR(jb, tile, s_count - 1u, 1);
-                const float sum0 = half_exp<true>(ua, ub, sl2, -rs.m, pw);
+                load_chunk(tS, 1, u1);
+                exp32<true>(u0, pw, s2, nf, acc0, acc1, top);
+                land_chunk(u1);
+                load_chunk(tS, 2, u0);
+                exp32<true>(u1, pw + 16, s2, nf, acc0, acc1, top);
+                land_chunk(u0);
+                load_chunk(tS, 3, u1);
+                if (kEarlyChunks >= 3) exp32<true>(u0, pw + 32, s2, nf, acc0, acc1, top);
+                if (kEarlyChunks == 4) {
+                    land_chunk(u1);
+                    exp32<true>(u1, pw + 48, s2, nf, acc0, acc1, top);
+                }
+                const float sum0 = part_sum<true>(acc0, acc1, top);
                 if (tr) FV_TR(jb, tile, s_count - 1u, 2);
-                load_half(tS + 64u, ua, ub);  // on its way while the first half is handed over
                 if (__any_sync(kFullWarp, !(sum0 <= kGuard))) {
-                    land_half(ua, ub);        // (nothing may be in flight into registers when the call is made)
+                    if (kEarlyChunks < 4) land_chunk(u1);  // (nothing may be in flight into registers when the call is made)
                     hot = false;              // nothing of this tile is stored: the careful way, whole tile
+                } else if (kEarlyChunks == 4) {
+                    store_early(tS, pw);      // the whole of P in one hand-over
+                    publish(bt + Smem::p_ready, lane);
+                    if (tr) FV_TR(jb, tile, s_count - 1u, 6);
+                    rs.l += sum0;
                 } else {
-                    hand_over(tS, 0u, pw, bt + Smem::p_early, lane);
+                    store_early(tS, pw);
+                    publish(bt + Smem::p_early, lane);
                     if (tr) FV_TR(jb, tile, s_count - 1u, 3);
-                    land_half(ua, ub);
+                    acc0 = acc1 = pack_f32x2(0.f, 0.f);
+                    top = 0.f;
+                    if (kEarlyChunks == 2) exp32<true>(u0, pw + 32, s2, nf, acc0, acc1, top);
+                    land_chunk(u1);
                     if (tr) FV_TR(jb, tile, s_count - 1u, 4);
-                    const float sum1 = half_exp<true>(ua, ub, sl2, -rs.m, pw);
+                    exp32<true>(u1, pw + 48, s2, nf, acc0, acc1, top);
+                    const float sum1 = part_sum<true>(acc0, acc1, top);
                     if (tr) FV_TR(jb, tile, s_count - 1u, 5);
                     if (__any_sync(kFullWarp, !(sum1 <= kGuard))) {
-                        // The first half went out against the old reference and its product may be running:
+                        // The early part went out against the old reference and its product may be running:
                         // wait for it (the issuer signals every early product), then the careful way for the
-                        // second half, whose scores (columns 64-127 of S) are untouched.
+                        // late part, whose scores (columns kEarlyKeys-127 of S) are untouched.
                         rs.l += sum0;
                         if (!__all_sync(kFullWarp, wait(bt + Smem::pv_early, (s_count - 1u) & 1u))) return;
                         tc_fence_after();
                         careful_tile(tS, tO, bt, cols, sl2, true, true, lane, &rs);
                     } else {
-                        hand_over(tS, 32u, pw, bt + Smem::p_ready, lane);
+                        store_late(tS, pw);
+                        publish(bt + Smem::p_ready, lane);
                         if (tr) FV_TR(jb, tile, s_count - 1u, 6);
                         rs.l += sum0 + sum1;
                     }
@@ -681,7 +726,7 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
 template <bool MASKED>
 FV_DEV void loader_thread(const CUtensorMap* mq, const CUtensorMap* mk, const CUtensorMap* mv, const Job& jb,
                           uint32_t sbase, const Waiter& wait) {
-    uint32_t qn = 0, kvn = 0;  // Q tiles and K/V tiles loaded so far
+    uint32_t qn = 0, kvn = 0;  // Q tiles and K/V pairs loaded so far
     tma_prefetch_desc(mq);
     tma_prefetch_desc(mk);
     tma_prefetch_desc(mv);
@@ -698,13 +743,21 @@ FV_DEV void loader_thread(const CUtensorMap* mq, const CUtensorMap* mk, const CU
         qn++;
         return true;
     };
-    auto load_kv = [&](const CUtensorMap* map, const KeyTile& kt, int plane) -> bool {
-        const uint32_t slot = kvn % kKvSlots, use = kvn / kKvSlots;
+    // Pair number p of the run lives in pair slot p % kKvPairs: first tile V of the previous key tile (absent in
+    // an item's first pair), second tile K of this key tile (absent in its last pair).  One barrier per pair.
+    auto load_pair = [&](const KeyTile* vt, const KeyTile* kt, int plane) -> bool {
+        const uint32_t slot = kvn % kKvPairs, use = kvn / kKvPairs;
         if (use > 0 && !wait(sbase + Smem::kv_free + 8u * slot, (use - 1u) & 1u)) return false;
-        const uint32_t dst = sbase + Smem::kv + slot * kSlotBytes, bar = sbase + Smem::kv_full + 8u * slot;
-        mbar_expect_tx(bar, kSlotBytes);
-        tma_load4(dst, map, bar, 0, kt.t * kKeyTile, plane, kt.seg);
-        tma_load4(dst + kPanelBytes, map, bar, 64, kt.t * kKeyTile, plane, kt.seg);
+        const uint32_t dst = sbase + Smem::kv + slot * 2u * kSlotBytes, bar = sbase + Smem::kv_full + 8u * slot;
+        mbar_expect_tx(bar, (vt ? kSlotBytes : 0u) + (kt ? kSlotBytes : 0u));
+        if (vt) {
+            tma_load4(dst, mv, bar, 0, vt->t * kKeyTile, plane, vt->seg);
+            tma_load4(dst + kPanelBytes, mv, bar, 64, vt->t * kKeyTile, plane, vt->seg);
+        }
+        if (kt) {
+            tma_load4(dst + kSlotBytes, mk, bar, 0, kt->t * kKeyTile, plane, kt->seg);
+            tma_load4(dst + kSlotBytes + kPanelBytes, mk, bar, 64, kt->t * kKeyTile, plane, kt->seg);
+        }
         kvn++;
         return true;
     };
@@ -721,7 +774,14 @@ FV_DEV void loader_thread(const CUtensorMap* mq, const CUtensorMap* mk, const CU
         const Span sp = span_of<MASKED>(jb, global_row(jb, it.q0), global_row(jb, min(it.q0 + kItemRows, jb.sq) - 1));
         KeyWalk<MASKED> walk;
         KeyTile kt;
-        while (ok && walk.next(jb, sp, kt)) ok = load_kv(mk, kt, it.plane) && load_kv(mv, kt, it.plane);
+        KeyTile prev;
+        bool have_prev = false;
+        while (ok && walk.next(jb, sp, kt)) {
+            ok = load_pair(have_prev ? &prev : nullptr, &kt, it.plane);
+            prev = kt;
+            have_prev = true;
+        }
+        if (ok && have_prev) ok = load_pair(&prev, nullptr, it.plane);
         // Tile B of the next item takes the slot of this item's tile A, free after its last Q.K^T.
         if (ok && nxt >= 0) ok = load_q(nxt, 1);
     }
@@ -731,9 +791,9 @@ FV_DEV void loader_thread(const CUtensorMap* mq, const CUtensorMap* mk, const CU
         const uint32_t last = ((qn - 1u - s) / kQSlots) * kQSlots + s;  // last load that used slot s
         mbar_drain(sbase + Smem::q_full + 8u * s, (last / kQSlots) & 1u);
     }
-    for (uint32_t s = 0; s < (uint32_t)kKvSlots && s < kvn; s++) {
-        const uint32_t last = ((kvn - 1u - s) / kKvSlots) * kKvSlots + s;
-        mbar_drain(sbase + Smem::kv_full + 8u * s, (last / kKvSlots) & 1u);
+    for (uint32_t s = 0; s < (uint32_t)kKvPairs && s < kvn; s++) {
+        const uint32_t last = ((kvn - 1u - s) / kKvPairs) * kKvPairs + s;
+        mbar_drain(sbase + Smem::kv_full + 8u * s, (last / kKvPairs) & 1u);
     }
 }
 
@@ -751,22 +811,32 @@ FV_DEV uint32_t kv_slot_addr(uint32_t sbase, uint32_t c) { return sbase + Smem::
 FV_DEV bool issue_output(const Job& jb, uint32_t sbase, uint32_t t, uint32_t tmem, uint64_t vd, bool fresh, uint32_t pc,
                          const Waiter& wait) {
     const uint32_t bt = sbase + 8u * t, tO = tmem + tmem_output(t), tP = tmem + tmem_scores(t);
-    if (!wait(bt + Smem::p_early, pc & 1u)) return false;
-    FV_TR(jb, 2, pc, 1 + 3 * t);
-    tc_fence_after();
-    output_mma_early(tO, tP, vd, fresh);
-    umma_commit(bt + Smem::pv_early);
+    if (kEarlyKeys < 128) {
+        if (!wait(bt + Smem::p_early, pc & 1u)) return false;
+        FV_TR(jb, 2, pc, 1 + 3 * t);
+        tc_fence_after();
+        output_mma_early(tO, tP, vd, fresh);
+        umma_commit(bt + Smem::pv_early);
+    }
     if (!wait(bt + Smem::p_ready, pc & 1u)) return false;
     FV_TR(jb, 2, pc, 2 + 3 * t);
     tc_fence_after();
-    output_mma_late(tO, tP, vd);
+    if (kEarlyKeys == 128) output_mma_early(tO, tP, vd, fresh);
+    else output_mma_late(tO, tP, vd);
     return true;
 }
 
+// The issuer: one thread, strictly in order.  Step j of an item (j = 0 .. n) is, for row tile t = A then B:
+// O_t += P_t(j-1) . V(j-1) for j > 0, then S_t = Q_t . K(j)^T for j < n.  The K/V ring is used in pairs
+// [V(j-1) | K(j)]: ONE wait for the pair's arrival and ONE commit that frees it per step, because every wait and
+// every commit is a point where this thread can stall while the tensor pipe's short queue runs dry.
+// (Two issuer threads, one per row tile, were tried: the two tiles' softmaxes then run in phase, share the MUFU
+// pipe for their whole length and the products wait for both -- 20 % slower.  The single in-order thread is what
+// keeps the tiles half a period apart.)
 template <bool MASKED>
 FV_DEV void issuer_thread(const Job& jb, uint32_t sbase, uint32_t tmem, const Waiter& wait) {
     uint32_t qn = 0;   // Q tiles consumed (two per item)
-    uint32_t kc = 0;   // K/V tiles consumed
+    uint32_t pn = 0;   // K/V pairs consumed
     uint32_t pc = 0;   // P tiles consumed per row tile
     Deal deal;
     for (int i = deal.next(jb); i >= 0; i = deal.next(jb)) {
@@ -789,25 +859,19 @@ FV_DEV void issuer_thread(const Job& jb, uint32_t sbase, uint32_t tmem, const Wa
         bool ok = true;
 #pragma unroll 1
         for (int j = 0; j <= n; j++) {
-            // step j: O_t += P_t(j-1) . V(j-1) for j > 0, then S_t = Q_t . K(j)^T for j < n; t = A, B
-            uint64_t vd = 0, kd = 0;
-            if (j > 0) {  // V(j-1) was loaded before K(j): the products that need it go first
-                if (!wait(sbase + Smem::kv_full + 8u * ((kc - 1u) % kKvSlots), ((kc - 1u) / kKvSlots) & 1u)) { ok = false; break; }
-                vd = umma_desc_sw128(kv_slot_addr(sbase, kc - 1u), kPanelBytes, 1024);
-                tc_fence_after();
-                FV_TR(jb, 2, pc, 0);
-            }
-            if (j < n) kd = umma_desc_sw128(kv_slot_addr(sbase, kc), 16, 1024);
+            const uint32_t slot = pn % kKvPairs;
+            const uint32_t pair = sbase + Smem::kv + slot * 2u * kSlotBytes;  // V(j-1) in its first tile, K(j) in its second
+            if (!wait(sbase + Smem::kv_full + 8u * slot, (pn / kKvPairs) & 1u)) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t vd = umma_desc_sw128(pair, kPanelBytes, 1024);
+            const uint64_t kd = umma_desc_sw128(pair + kSlotBytes, 16, 1024);
+            if (j > 0) FV_TR(jb, 2, pc, 0);
 #pragma unroll
             for (uint32_t t = 0; t < 2; t++) {
                 if (j > 0 && !issue_output(jb, sbase, t, tmem, vd, j == 1, pc, wait)) { ok = false; break; }
                 if (j == n) {
                     umma_commit(sbase + Smem::o_ready + 8u * t);
                     continue;
-                }
-                if (t == 0) {
-                    if (!wait(sbase + Smem::kv_full + 8u * (kc % kKvSlots), (kc / kKvSlots) & 1u)) { ok = false; break; }
-                    tc_fence_after();
                 }
                 if (j == 0) {  // (tile B of an item is loaded late, see loader_thread: it is waited for where it is first used)
                     if (!wait(sbase + Smem::q_full + 8u * (t ? qb : qa), t ? qb_par : qa_par)) { ok = false; break; }
@@ -819,14 +883,9 @@ FV_DEV void issuer_thread(const Job& jb, uint32_t sbase, uint32_t tmem, const Wa
                 if (j == n - 1) umma_commit(sbase + Smem::q_free + 8u * (t ? qb : qa));
             }
             if (!ok) break;
-            if (j > 0) {
-                umma_commit(sbase + Smem::kv_free + 8u * ((kc - 1u) % kKvSlots));
-                pc++;
-            }
-            if (j < n) {
-                umma_commit(sbase + Smem::kv_free + 8u * (kc % kKvSlots));
-                kc += 2;   // K(j) and, next step, V(j)
-            }
+            umma_commit(sbase + Smem::kv_free + 8u * slot);
+            pn++;
+            if (j > 0) pc++;
         }
         if (!ok) break;
     }

@@ -223,6 +223,16 @@ FV_DEV void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
         : "memory");
 }
 
+// Store r[OFF .. OFF+15] to 16 consecutive TMEM columns of this thread's lane.
+template <int OFF, int N>
+FV_DEV void tmem_st16_at(uint32_t taddr, const uint32_t (&r)[N]) {
+    static_assert(OFF + 16 <= N, "tmem_st16_at: out of range");
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), FV_I16(r, OFF)
+        : "memory");
+}
+
 // --------------------------------------------------------------------- math
 FV_DEV float ex2(float x) {
     float y;

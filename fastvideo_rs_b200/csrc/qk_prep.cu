@@ -33,6 +33,8 @@ struct Params {
     int batch, seq, heads, width, col_q, col_k, col_v;
     float eps;
     int per_head;
+    int kv_rows, kv_row0;       // k_out / v_out planes have kv_rows token rows and token s lands in row kv_row0 + s
+                                // (kv_rows = seq, kv_row0 = 0: plain BHSD; otherwise the tail of a K/V cache)
 };
 
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
@@ -86,10 +88,11 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_kernel(const Params
     const int h = act ? (8 * t) / kD : 0, pd = act ? (8 * t) % kD : 0;
     const __nv_bfloat16* src = p.proj + (size_t)row * p.width;
     const size_t dst = (((size_t)b * p.heads + h) * p.seq + s) * kD + pd;
+    const size_t dst_kv = (((size_t)b * p.heads + h) * p.kv_rows + p.kv_row0 + s) * kD + pd;
 
     if (p.v_out && act) {
         const uint4 v = *reinterpret_cast<const uint4*>(src + p.col_v + 8 * t);
-        *reinterpret_cast<uint4*>(p.v_out + dst) = v;
+        *reinterpret_cast<uint4*>(p.v_out + dst_kv) = v;
     }
     // Everything the row needs is requested before the reduction, so the kernel pays one memory round trip, not three:
     // rope factors (cos at the even index, sin at the odd one of each pair; the tables repeat each value twice) and weights.
@@ -135,7 +138,7 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_kernel(const Params
         denom = (float)(p.heads * kD);
     }
     if (!act) return;
-    auto finish = [&](const float (&x)[8], float ss, const float (&wv)[8], __nv_bfloat16* out) {
+    auto finish = [&](const float (&x)[8], float ss, const float (&wv)[8], __nv_bfloat16* out, size_t dst) {
         const float ms = __fdiv_rn(ss, denom);
         const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, p.eps)));
         float y[8];
@@ -156,8 +159,8 @@ __global__ void __launch_bounds__(MAXT, MINB) fv_wan_qk_prep_kernel(const Params
         *reinterpret_cast<uint4*>(out + dst) =
             make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
     };
-    if (p.q_out) finish(xq, sq, wqv, p.q_out);
-    if (p.k_out) finish(xk, sk, wkv, p.k_out);
+    if (p.q_out) finish(xq, sq, wqv, p.q_out, dst);
+    if (p.k_out) finish(xk, sk, wkv, p.k_out, dst_kv);
 }
 
 
@@ -209,7 +212,7 @@ __global__ void __launch_bounds__(32 * G * NG, MINB) fv_wan_qk_prep_group_kernel
             for (int j = 0; j < J; j++) {
                 const int c = g + 32 * G * j;
                 if (c < chunks)
-                    *reinterpret_cast<uint4*>(p.v_out + (((size_t)b * p.heads + (c >> 4)) * p.seq + s) * kD + pd) = vv[j];
+                    *reinterpret_cast<uint4*>(p.v_out + (((size_t)b * p.heads + (c >> 4)) * p.kv_rows + p.kv_row0 + s) * kD + pd) = vv[j];
             }
         } else {
 #pragma unroll
@@ -263,8 +266,9 @@ __global__ void __launch_bounds__(32 * G * NG, MINB) fv_wan_qk_prep_group_kernel
         for (int j = 0; j < J; j++) {
             const int c = g + 32 * G * j;
             if (c >= chunks) continue;
-            const size_t dst = (((size_t)b * p.heads + (c >> 4)) * p.seq + s) * kD + pd;
-            auto finish = [&](const uint4& raw, float ss, const float* wsrc, __nv_bfloat16* out) {
+            const size_t plane = (size_t)b * p.heads + (c >> 4);
+            const size_t dst_q = (plane * p.seq + s) * kD + pd, dst_kv = (plane * p.kv_rows + p.kv_row0 + s) * kD + pd;
+            auto finish = [&](const uint4& raw, float ss, const float* wsrc, __nv_bfloat16* out, size_t dst) {
                 float x[8];
                 unpack8(raw, x);
                 const float4 w0 = __ldg(reinterpret_cast<const float4*>(wsrc + 8 * c)), w1 = __ldg(reinterpret_cast<const float4*>(wsrc + 8 * c + 4));
@@ -288,8 +292,8 @@ __global__ void __launch_bounds__(32 * G * NG, MINB) fv_wan_qk_prep_group_kernel
                 *reinterpret_cast<uint4*>(out + dst) =
                     make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
             };
-            if (p.q_out) finish(vq[j], p.per_head ? sq[j] : tq, p.wq, p.q_out);
-            if (p.k_out) finish(vk[j], p.per_head ? sk[j] : tk, p.wk, p.k_out);
+            if (p.q_out) finish(vq[j], p.per_head ? sq[j] : tq, p.wq, p.q_out, dst_q);
+            if (p.k_out) finish(vk[j], p.per_head ? sk[j] : tk, p.wk, p.k_out, dst_kv);
         }
     }
 }
@@ -315,10 +319,33 @@ int launch_group(const Params& p, long long rows, int j_need, int sms, cudaStrea
 
 }  // namespace fvprep
 
+static int qk_prep_impl(void* stream, const void* proj, int width, int col_q, int col_k, int col_v, const float* wq,
+                        const float* wk, const float* cosv, const float* sinv, int batch, int seq, int heads, int d, float eps,
+                        int norm_scope, void* q_out, void* k_out, void* v_out, int kv_rows, int kv_row0);
+
 extern "C" int fv_wan_qk_prep_bf16(void* stream, const void* proj, int width, int col_q, int col_k, int col_v,
                                    const float* wq, const float* wk, const float* cosv, const float* sinv, int batch,
                                    int seq, int heads, int d, float eps, int norm_scope, void* q_out, void* k_out,
                                    void* v_out) {
+    return qk_prep_impl(stream, proj, width, col_q, col_k, col_v, wq, wk, cosv, sinv, batch, seq, heads, d, eps, norm_scope, q_out,
+                        k_out, v_out, seq, 0);
+}
+
+extern "C" int fv_wan_qk_prep_cache_bf16(void* stream, const void* proj, int width, int col_q, int col_k, int col_v,
+                                         const float* wq, const float* wk, const float* cosv, const float* sinv, int batch,
+                                         int seq, int heads, int d, float eps, int norm_scope, void* q_out, void* k_cache,
+                                         void* v_cache, int cache_rows, int cache_row0) {
+    if (cache_rows <= 0 || cache_row0 < 0 || (long long)cache_row0 + seq > cache_rows) {
+        fvrt::clear_error();
+        return fvrt::fail(FV_ERR_INVALID, "qk_prep: %d tokens at row %d do not fit a cache of %d rows", seq, cache_row0, cache_rows);
+    }
+    return qk_prep_impl(stream, proj, width, col_q, col_k, col_v, wq, wk, cosv, sinv, batch, seq, heads, d, eps, norm_scope, q_out,
+                        k_cache, v_cache, cache_rows, cache_row0);
+}
+
+static int qk_prep_impl(void* stream, const void* proj, int width, int col_q, int col_k, int col_v, const float* wq,
+                        const float* wk, const float* cosv, const float* sinv, int batch, int seq, int heads, int d, float eps,
+                        int norm_scope, void* q_out, void* k_out, void* v_out, int kv_rows, int kv_row0) {
     fvrt::clear_error();
     if (d != 128 || batch <= 0 || seq <= 0 || heads <= 0 || heads > 64) return FV_DECLINED;
     if ((long long)batch * seq > 0x7fffffffll) return FV_DECLINED;
@@ -355,6 +382,8 @@ extern "C" int fv_wan_qk_prep_bf16(void* stream, const void* proj, int width, in
     p.col_v = col_v;
     p.eps = eps;
     p.per_head = norm_scope == FV_NORM_PER_HEAD;
+    p.kv_rows = kv_rows;
+    p.kv_row0 = kv_row0;
     const int threads = (heads * 16 + 31) & ~31;
     const char* which = getenv("FV_PREP_KERNEL");  // "row": the one-CTA-per-row kernel (A/B timing and the bit-equality test)
     if (!which || which[0] != 'r') {

@@ -39,10 +39,13 @@ def wan_rope_tables(grid, d: int = 128, theta: float = 10000.0, start_frame: int
 def qk_prep(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], cos: Optional[torch.Tensor],
             sin: Optional[torch.Tensor], heads: int, col_q: int = 0, col_k: Optional[int] = None,
             col_v: Optional[int] = None, eps: float = 1e-6, norm_scope: int = NORM_ACROSS_HEADS,
-            want_q: bool = True, want_k: bool = True, want_v: bool = True):
+            want_q: bool = True, want_k: bool = True, want_v: bool = True, cache=None):
     """RMSNorm * w, RoPE, head split of q and k (and the head split of v) in one pass over the fused
     projection `proj` [batch, seq, width] bf16.  Default column layout is [q | k | v].  Returns
-    (q, k, v) as [batch, heads, seq, 128] bf16 tensors (None for the ones not asked for)."""
+    (q, k, v) as [batch, heads, seq, 128] bf16 tensors (None for the ones not asked for).
+    cache = (k_cache, v_cache, row0): K and V of the block go straight into rows [row0, row0 + seq) of the
+    [batch, heads, cache_rows, 128] bf16 cache tensors (the append of wan/causal.rs:541-628 without its two
+    copies); k and v of the result are then views of those rows."""
     if not proj.is_cuda or proj.dtype != torch.bfloat16 or not proj.is_contiguous() or proj.dim() != 3:
         raise ValueError("qk_prep: proj must be a contiguous CUDA bf16 [batch, seq, width] tensor")
     b, seq, width = proj.shape
@@ -51,8 +54,27 @@ def qk_prep(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.T
     col_k = dim if col_k is None else col_k
     col_v = 2 * dim if col_v is None else col_v
     mk = lambda want: torch.empty((b, heads, seq, d), dtype=torch.bfloat16, device=proj.device) if want else None
-    q, k, v = mk(want_q), mk(want_k), mk(want_v)
     ptr = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+    if cache is not None:
+        kc, vc, row0 = cache
+        for n, t in (("k_cache", kc), ("v_cache", vc)):
+            if t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous() or t.dim() != 4 or \
+                    t.shape[0] != b or t.shape[1] != heads or t.shape[3] != d:
+                raise ValueError(f"qk_prep: {n} must be a contiguous CUDA bf16 [batch, heads, rows, 128] tensor")
+        if kc.shape != vc.shape:
+            raise ValueError("qk_prep: k_cache and v_cache differ in shape")
+        q = mk(want_q)
+        for name, t in (("wq", wq), ("wk", wk), ("cos", cos), ("sin", sin)):
+            if t is not None and (t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous()):
+                raise ValueError(f"qk_prep: {name} must be a contiguous CUDA float32 tensor")
+        fp = lambda t: ctypes.cast(ctypes.c_void_p(t.data_ptr()), _f32p) if t is not None else None
+        with torch.cuda.device(proj.device):
+            rc = _lib.lib().fv_wan_qk_prep_cache_bf16(_stream_ptr(), ptr(proj), width, col_q, col_k, col_v, fp(wq), fp(wk),
+                                                      fp(cos), fp(sin), b, seq, heads, d, ctypes.c_float(eps), norm_scope,
+                                                      ptr(q), ptr(kc), ptr(vc), kc.shape[2], int(row0))
+        _lib.check(rc, "qk_prep (cache)")
+        return q, kc[:, :, row0:row0 + seq], vc[:, :, row0:row0 + seq]
+    q, k, v = mk(want_q), mk(want_k), mk(want_v)
     fptr = lambda t: ctypes.cast(ctypes.c_void_p(t.data_ptr()), _f32p) if t is not None else None
     for name, t in (("wq", wq), ("wk", wk), ("cos", cos), ("sin", sin)):
         if t is not None and (t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous()):
@@ -126,6 +148,31 @@ class WanSelfAttention:
             from .sdpa import dense_fwd_merged
             return dense_fwd_merged(q, k, v, scale=scale)
         return sdpa(q, k, v, Plan.dense(scale))
+
+
+def rope_bhsd(src: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, dst: torch.Tensor, *, src_row0: int = 0,
+              dst_row0: int = 0, negate_sin: bool = False) -> torch.Tensor:
+    """Wan's interleaved RoPE over rows of BHSD tensors (rope_bhsd_f32 / rope_bhsd, wan/causal.rs:246-275, and the
+    copy_tokens that follows it in KvRope::RebasedSink, :734-812): rows [src_row0, src_row0 + n) of src
+    [b, h, rows, 128] (bf16 or f32) rotated with table rows 0 .. n-1 of cos / sin [n, 128] f32 into rows
+    [dst_row0, dst_row0 + n) of dst (bf16 or f32).  negate_sin rotates back.  Returns dst."""
+    n = cos.shape[0]
+    for name, t in (("src", src), ("dst", dst)):
+        if not t.is_cuda or t.dtype not in (torch.bfloat16, torch.float32) or not t.is_contiguous() or t.dim() != 4 or t.shape[3] != 128:
+            raise ValueError(f"rope_bhsd: {name} must be a contiguous CUDA bf16 or float32 [b, h, rows, 128] tensor")
+    if src.shape[:2] != dst.shape[:2] or cos.shape != (n, 128) or sin.shape != (n, 128):
+        raise ValueError("rope_bhsd: shapes")
+    for name, t in (("cos", cos), ("sin", sin)):
+        if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"rope_bhsd: {name} must be a contiguous CUDA float32 tensor")
+    fp = lambda t: ctypes.cast(ctypes.c_void_p(t.data_ptr()), _f32p)
+    with torch.cuda.device(src.device):
+        rc = _lib.lib().fv_wan_rope_bhsd(_stream_ptr(), ctypes.c_void_p(src.data_ptr()), int(src.dtype == torch.bfloat16),
+                                         src.shape[2], int(src_row0), fp(cos), fp(sin), int(negate_sin),
+                                         src.shape[0] * src.shape[1], n, ctypes.c_void_p(dst.data_ptr()),
+                                         int(dst.dtype == torch.bfloat16), dst.shape[2], int(dst_row0))
+    _lib.check(rc, "rope_bhsd")
+    return dst
 
 
 def ln_adaln_e(x: torch.Tensor, e: torch.Tensor, scale_slot: int, shift_slot: int, eps: float = 1e-6) -> torch.Tensor:

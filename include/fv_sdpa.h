@@ -204,6 +204,29 @@ FV_API int fv_wan_rope_tables(int ppf, int pph, int ppw, int d, double theta, in
  * vsa_attention_device (:358-470) with its launchers (rt/ops.rs:811-923,1074-1383,1554-1619;
  * rt/attn_dc.rs:275-604); arithmetic of the host twin vsa_attention_host (rt/vsa.rs:116-262). */
 
+/* ---- the causal K/V cache's device work (Self-Forcing inference) ---------------------------------------
+ * fv_wan_qk_prep_cache_bf16 is fv_wan_qk_prep_bf16 whose K and V land in the cache: k_cache / v_cache are
+ * [batch * heads, cache_rows, 128] bf16 and token s of the block is written at row cache_row0 + s (q_out stays
+ * [batch * heads, seq, 128]).  It replaces the prologue plus the two copy_tokens launches with which the
+ * reference appends a block to its cache (crates/fastvideo-cudarc/src/wan/causal.rs:194-236,541-628; caller
+ * wan/transformer.rs:290-313).  Errors: block does not fit the cache.
+ *
+ * fv_wan_rope_bhsd rotates n rows of every plane with Wan's interleaved-pair RoPE: source rows
+ * [src_row0, src_row0 + n) of planes of src_plane_rows rows, table rows 0 .. n-1 (cos, sin f32 [n, 128], each
+ * value twice), destination rows [dst_row0, dst_row0 + n) of planes of dst_plane_rows rows; source and
+ * destination bf16 or f32 each; negate_sin rotates back.  One launch in place of rope_bhsd_f32 + quantize_bf16 +
+ * copy_tokens of KvRope::RebasedSink (wan/causal.rs:246-275,734-812): un-roped copy of the sink = (cache K bf16,
+ * own tables, negate_sin = 1) -> f32 buffer; re-roped sink = (that buffer, the target frames' tables) -> cache K rows
+ * [0, sink).  Arithmetic of the host twin apply_rotary_bshd (rt/ops.rs:1903-1933): products and sums rounded
+ * separately, one rounding to bf16.  Source and destination may be the same rows.  Declines: empty sizes. */
+FV_API int fv_wan_qk_prep_cache_bf16(void* stream, const void* proj, int width, int col_q, int col_k, int col_v,
+                                     const float* wq, const float* wk, const float* cosv, const float* sinv, int batch,
+                                     int seq, int heads, int d, float eps, int norm_scope, void* q_out, void* k_cache,
+                                     void* v_cache, int cache_rows, int cache_row0);
+FV_API int fv_wan_rope_bhsd(void* stream, const void* src, int src_is_bf16, int src_plane_rows, int src_row0,
+                            const float* cosv, const float* sinv, int negate_sin, int planes, int n, void* dst,
+                            int dst_is_bf16, int dst_plane_rows, int dst_row0);
+
 /* ---- operand rounding for f32-stored activations ------------------------------------------------
  * The reference rounds q, k, v to bf16 before its attention kernels under bf16 activations and rounds the
  * result again (act16_operands and the tail of dense, crates/fastvideo-cudarc/src/rt/sdpa.rs:167-181,184-214:

@@ -319,6 +319,20 @@ def vsa_attention_host(q, k, v, gate, grid, topk, scale=None, want_aux=False):
 
 
 # --------------------------------------------------------------------------- block glue
+def rope_bhsd(x, cos, sin, negate_sin: bool = False) -> np.ndarray:
+    """apply_rotary_bshd on BHSD rows (C/rt/ops.rs:1903-1933 through rope_bhsd_f32, C/wan/causal.rs:246-263):
+    x [planes, n, d] f32, cos / sin [n, d]; pairs (2i, 2i+1) use the tables' even index; products and sums
+    rounded separately in f32.  Result f32."""
+    x = _f32(x)
+    c = _f32(cos)[None, :, 0::2]
+    s = _f32(sin)[None, :, 0::2] * np.float32(-1.0 if negate_sin else 1.0)
+    x0, x1 = x[..., 0::2], x[..., 1::2]
+    out = np.empty_like(x)
+    out[..., 0::2] = (x0 * c).astype(np.float32) - (x1 * s).astype(np.float32)
+    out[..., 1::2] = (x0 * s).astype(np.float32) + (x1 * c).astype(np.float32)
+    return out
+
+
 def ln_adaln_e(x, e, scale_slot: int, shift_slot: int, eps: float = 1e-6) -> np.ndarray:
     """Unaffine LayerNorm + AdaLN modulation, f32 (C/rt/kernels/act16.cu:184-209, mx_ln_adaln_e):
     x [batch, seq, dim], e [batch, e_rows, dim] -> (x - mean) * rsqrt(var + eps) * (1 + e[b, scale]) + e[b, shift],

@@ -121,3 +121,65 @@ def test_prep_slab_of_wan14b_rows(fvlib, oracle):
         g = to_host_f32(got[:, :, tt]).reshape(heads, len(tok), 128)
         assert np.mean(g != oracle.bf16_round(want)) < 2e-3
         assert np.abs(g - want).max() <= np.abs(want).max() * 2.0 ** -8
+
+
+def test_prep_writes_the_block_into_the_cache_tail(fvlib, oracle):
+    """fv_wan_qk_prep_cache_bf16: K and V of a block land in rows [row0, row0 + seq) of the cache planes, bit for
+    bit what the plain call plus two copies give (the append of wan/causal.rs:541-628); other rows untouched."""
+    from fastvideo_rs_b200 import wan
+    batch, heads, grid, cap, row0 = 2, 12, (1, 6, 13), 300, 150
+    seq, dim = grid[0] * grid[1] * grid[2], heads * 128
+    proj = to_dev_bf16(oracle.bf16_round(oracle.seeded_normal(35, 0, (batch, seq, 3 * dim))))
+    w = torch.from_numpy((1.0 + 0.1 * oracle.seeded_normal(35, 1, (dim,))).astype(np.float32)).cuda()
+    tc, ts = wan.wan_rope_tables(grid)
+    q0, k0, v0 = wan.qk_prep(proj, w, w, tc, ts, heads)
+    kc = torch.full((batch, heads, cap, 128), 7.0, dtype=torch.bfloat16, device="cuda")
+    vc = torch.full_like(kc, -3.0)
+    q1, k1, v1 = wan.qk_prep(proj, w, w, tc, ts, heads, cache=(kc, vc, row0))
+    assert torch.equal(q0, q1) and torch.equal(k0, k1) and torch.equal(v0, v1)
+    assert torch.equal(kc[:, :, row0:row0 + seq], k0) and torch.equal(vc[:, :, row0:row0 + seq], v0)
+    assert (kc[:, :, :row0] == 7.0).all() and (kc[:, :, row0 + seq:] == 7.0).all()
+    assert (vc[:, :, :row0] == -3.0).all() and (vc[:, :, row0 + seq:] == -3.0).all()
+    for kern in ("row",):
+        import os
+        os.environ["FV_PREP_KERNEL"] = kern
+        try:
+            kc2 = torch.zeros_like(kc)
+            wan.qk_prep(proj, w, w, tc, ts, heads, cache=(kc2, torch.zeros_like(vc), cap - seq))
+        finally:
+            del os.environ["FV_PREP_KERNEL"]
+        assert torch.equal(kc2[:, :, cap - seq:], k0)
+    with pytest.raises(Exception):
+        wan.qk_prep(proj, w, w, tc, ts, heads, cache=(kc, vc, cap - seq + 1))
+
+
+def test_rope_bhsd_rebases_a_sink(fvlib, oracle):
+    """fv_wan_rope_bhsd against the oracle's apply_rotary twin: f32 results bit for bit, bf16 results = RNE of
+    those; and the rebased-sink sequence of wan/causal.rs:734-812 -- un-rope the cached sink keys with their own
+    tables (sin negated) into an f32 buffer, rope that buffer at the target frames into the cache head."""
+    from fastvideo_rs_b200 import wan
+    b, h, cap, sink = 1, 3, 500, 2 * 78
+    grid = (6, 6, 13)   # 78 tokens per frame
+    cos, sin = oracle.wan_rope(*grid)
+    own = slice(0, sink)             # the sink's own frames 0, 1
+    new = slice(3 * 78, 3 * 78 + sink)  # target frames 3, 4
+    x = oracle.bf16_round(oracle.seeded_normal(36, 0, (b * h, cap, 128)))
+    kc = to_dev_bf16(x).view(b, h, cap, 128).clone()
+    tco, tso = torch.from_numpy(cos[own].copy()).cuda(), torch.from_numpy(sin[own].copy()).cuda()
+    tcn, tsn = torch.from_numpy(cos[new].copy()).cuda(), torch.from_numpy(sin[new].copy()).cuda()
+    raw = torch.empty((b, h, sink, 128), dtype=torch.float32, device="cuda")
+    wan.rope_bhsd(kc, tco, tso, raw, negate_sin=True)
+    want_raw = oracle.rope_bhsd(x[:, :sink], cos[own], sin[own], negate_sin=True)
+    assert np.array_equal(raw.cpu().numpy().reshape(b * h, sink, 128), want_raw)
+    wan.rope_bhsd(raw, tcn, tsn, kc)
+    want_head = oracle.bf16_round(oracle.rope_bhsd(want_raw, cos[new], sin[new]))
+    got = to_host_f32(kc).reshape(b * h, cap, 128)
+    assert np.array_equal(got[:, :sink], want_head)
+    assert np.array_equal(got[:, sink:], x[:, sink:])
+    # rows in the middle of both tensors, bf16 -> bf16 in place
+    mid = kc.clone()
+    wan.rope_bhsd(mid, tcn, tsn, mid, src_row0=200, dst_row0=200)
+    want_mid = oracle.bf16_round(oracle.rope_bhsd(got[:, 200:200 + sink], cos[new], sin[new]))
+    assert np.array_equal(to_host_f32(mid).reshape(b * h, cap, 128)[:, 200:200 + sink], want_mid)
+    with pytest.raises(Exception):
+        wan.rope_bhsd(kc, tcn, tsn, raw, src_row0=cap - sink + 1)

@@ -278,3 +278,24 @@ def test_block_glue_twins_closed_form(oracle):
     g = np.ones((1, 6, 64), np.float32)
     hid1, n1 = oracle.self_residual_norm(h1, a1, g, 2, np.ones(64, np.float32), np.zeros(64, np.float32))
     assert np.array_equal(hid1, h1) and np.abs(n1).min() > 0.2  # 2^-12 / sqrt(2^-24 + eps)
+
+
+def test_rope_bhsd_twin_follows_the_host_loop(oracle):
+    """apply_rotary_bshd (C/rt/ops.rs:1903-1933) restated as the plain loop on a small case, against the
+    vectorised twin; rotating back with the negated sine (C/wan/causal.rs:764-771) returns the input up to
+    one rounding."""
+    import numpy as np
+    cos, sin = oracle.wan_rope(2, 2, 3)
+    x = oracle.seeded_normal(77, 0, (3, 12, 128))
+    got = oracle.rope_bhsd(x, cos, sin)
+    want = np.empty_like(x)
+    for b in range(3):
+        for t in range(12):
+            for i in range(64):
+                x1, x2 = x[b, t, 2 * i], x[b, t, 2 * i + 1]
+                cs, sn = cos[t, 2 * i], sin[t, 2 * i]
+                want[b, t, 2 * i] = np.float32(x1 * cs) - np.float32(x2 * sn)
+                want[b, t, 2 * i + 1] = np.float32(x1 * sn) + np.float32(x2 * cs)
+    assert np.array_equal(got, want)
+    back = oracle.rope_bhsd(got, cos, sin, negate_sin=True)
+    assert np.abs(back - x).max() < 1e-6
