@@ -7,37 +7,37 @@
 // Shape of the kernel
 // -------------------
 // * One CTA per SM for the whole launch.  Work items (256 query rows of one plane = two 128-row
-//   accumulator tiles, "A" and "B") are dealt round-robin: CTA c takes items c, c + grid, ...
-//   Under a causal mask the items of a plane are ordered heaviest first.
+//   accumulator tiles, "A" and "B") are dealt in snake order: in round r CTA c takes item r G + c, in the
+//   next one item (r + 1) G + (G - 1 - c).  Under a mask the items are ordered heaviest first.
 // * 12 warps = three warpgroups.  The launch gives every thread 168 registers; the two softmax
 //   warpgroups then take 216 each and the third drops to 72 (256 x 216 + 128 x 72 = 384 x 168):
 //     warps 0-7    softmax: warp w serves row tile w / 4, TMEM lanes 32 (w % 4) .. + 31 (thread =
 //                  TMEM lane = query row, the only mapping the 32x32b TMEM load offers).
-//     warp 8       loader: one thread issues every TMA copy (Q ring of 3 x 32 KB, K/V ring of
-//                  4 x 32 KB) and runs one item ahead with the Q tiles.
+//     warp 8       loader: one thread issues every TMA copy (Q ring of 3 x 32 KB; K/V ring of 4 x 32 KB
+//                  filled in PAIRS [V(j-1) | K(j)], one barrier per pair) and runs one item ahead with
+//                  the Q tiles.
 //     warp 9       issuer: one thread issues every tcgen05.mma; the warp owns the TMEM allocation.
 //     warps 10-11  idle (they make the third warpgroup whole).
 // * TMEM (512 columns): scores S_A, S_B (128 f32 columns each), then the output accumulators O_A,
 //   O_B.  The bf16 probabilities P overwrite S from its column 0 on (64 columns), always behind the
-//   columns still to be read.  (With S and O of a tile side by side instead, the P.V products, which
-//   read P and update O at once, ran measurably slower.)
+//   columns still to be read.
 // * Per key tile j the issuer runs, for t = A then B:  O_t += P_t(j-1) . V(j-1);  S_t = Q_t . K(j)^T,
-//   so one row tile's softmax runs under the other's MMAs.  That only works while a softmax step is
-//   shorter than the other tile's two MMAs (1024 tensor-pipe cycles); a longer one makes both tiles'
-//   softmax warps run at the same time on the same schedulers, which doubles it again.  Hence:
-// * P is handed to the issuer in two steps (keys 0-63, then 64-127), so the first half of P.V runs while
-//   the second half of the exponentials is still being evaluated.
+//   strictly in order, so one row tile's softmax runs under the other's MMAs and the two tiles stay half a
+//   period apart (the MUFU pipe of a scheduler then serves one tile's exponentials at a time).  Per step the
+//   issuer waits three times (the K/V pair, P_A, P_B) and commits four times: every wait and commit is a
+//   point where it can stall while the tensor pipe's short queue runs dry, and halving their number (pairs
+//   instead of single tiles, P handed over whole instead of in two parts) was worth 9 % and 7 % of the
+//   step.  SM-clock stamps of one CTA's roles (a bring-up build, -DFV_ATT_TRACE) are how this was found.
 // * STREAMING softmax without a maximum pass.  Base-2 domain, lazy reference m per row: P = 2^(s -
 //   m) is evaluated straight away against the reference the row already has, 32 columns at a time as
-//   they come out of TMEM (loads double-buffered), and each half row's sum of P is the proof that this
-//   was safe: every P is positive, so sum(P) <= 2^40 implies max(P) <= 2^40, far inside what bf16 P and
-//   f32 accumulators hold, and a reference that lags the true maximum by any amount cancels exactly
-//   when O is divided by the row sum.  Only when a sum exceeds the guard (or the row has no reference
-//   yet: the first tile of an item) does the warp take the exact path: read S again (what it needs is
-//   still there), take the row maxima, move the references, rescale O and the row sums, evaluate P
-//   again; if it is the second half that trips, the first half is already with the issuer, and the warp
-//   waits for that product to finish before it touches O.  On N(0,1) inputs the exact path runs on the
-//   first tile of each item and nowhere else.
+//   they come out of TMEM (the next chunk's load in flight), a quarter of the exponentials on the FMA
+//   pipe, and the row's sum of P is the proof that this was safe: every P is positive, so sum(P) <= 2^40
+//   implies max(P) <= 2^40, far inside what bf16 P and f32 accumulators hold, and a reference that lags
+//   the true maximum by any amount cancels exactly when O is divided by the row sum.  Only when a sum
+//   exceeds the guard (or the row has no reference yet: the first tile of an item) does the warp take the
+//   exact path: nothing of the tile has been stored, so it reads S again, takes the row maxima, moves the
+//   references, rescales O and the row sums, evaluates P again.  On N(0,1) inputs the exact path runs on
+//   the first tile of each item and nowhere else.
 // * Every wait is bounded: a role that gives up records a code in the status word, raises the CTA's
 //   abort flag, and every role falls through to the common exit, where copies in flight are awaited,
 //   the issuer's last MMA is awaited and TMEM is freed.  No trap, no endless spin.
