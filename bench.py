@@ -305,13 +305,21 @@ class Bench:
         self.needs_flush = self.proj.numel() * 2 + 2 * self.bh * (self.window + self.cross) * 128 * 2 < 4 * 126e6
         self.flops = workload_flops(self.wl)
 
+    def remote_passes(self):
+        """Attention launches of one step after the local pass."""
+        if getattr(self.spa, "exchange", "nccl") != "ce":
+            # Python nccl exchange: one pass over everything the all-gather brought; the native handle: one remote pass
+            # per head group
+            return 1 if hasattr(self.spa, "exchange") else getattr(self.spa, "groups", 1)
+        return len(self.layout.source_groups(self.causal, self.spa.grouped))
+
     def launches_per_step(self):
         if self.vsa_topk:
             return 5
         if self.window:
             return 3 if self.split else 2  # prologue, attention, and the merge of the key ranges when the keys are cut
         if self.spa is not None:
-            return 2 + len(self.layout.source_order(self.causal))
+            return 2 + self.remote_passes()
         return 2
 
     def step(self, p, record=False, keep=False):
@@ -575,7 +583,7 @@ def main():
                 "L2 flushed between steps (512 MB written before each step, outside the per-step event pairs that are summed)"
             if world > 1:
                 cfg["sp"] = dict(impl=args.sp_impl, exchange=getattr(b.spa, "exchange", "nccl"), shards="zigzag" if b.layout.zigzag else "contiguous",
-                                 passes=1 + len(b.layout.source_order(b.causal)))
+                                 passes=1 + b.remote_passes())
         return cfg
 
     if args.impl == "reference":

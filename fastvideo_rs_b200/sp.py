@@ -158,6 +158,34 @@ class SpLayout:
         flags = self.needed(causal).get(src, [False] * self.nrun)
         return [l if f else 0 for (_, l), f in zip(self.runs[src], flags)], [s for s, _ in self.runs[src]]
 
+    def source_groups(self, causal: Optional[BlockCausal], grouped: bool = True) -> List[List[int]]:
+        """The needed sources in the order they are pulled, cut into the passes that consume them: one source, then
+        two, then four, ... (grouped) or one per pass.  A pass costs a fixed amount per work item (the first key tile
+        of an item takes the exact softmax path, the pipeline fills and drains, the epilogue reads and writes the f32
+        state), so at 8 ranks seven passes of one source each spend a fifth of their time there; doubling the group
+        keeps the first remote pass as early as it can be and every later one no longer than what hides its copies."""
+        order = self.source_order(causal)
+        if not grouped:
+            return [[s] for s in order]
+        groups, size, i = [], 1, 0
+        while i < len(order):
+            groups.append(order[i:i + size])
+            i += size
+            size *= 2
+        return groups
+
+    def group_segments(self, srcs, causal: Optional[BlockCausal]):
+        """(seg_len, seg_start) over the whole gathered buffer [world, runs, ...] with only the runs of `srcs` that
+        somebody here can see left non-empty."""
+        need = self.needed(causal)
+        lens, starts = [], []
+        for r in range(self.world):
+            flags = need.get(r, [False] * self.nrun)
+            for (s0, l), f in zip(self.runs[r], flags):
+                lens.append(l if (f and r in srcs and r != self.rank) else 0)
+                starts.append(s0)
+        return lens, starts
+
     def pass2(self):
         """(seg_len, seg_start) of ONE remote-keys pass over the whole gathered buffer [world, runs, ...]: every
         run at its global offset, this rank's own ones emptied (pass 1 covered them)."""
@@ -181,10 +209,10 @@ class SpAttention:
     """Sequence-parallel attention for one (seq, bh) shape; buffers allocated once.
 
     Per call: this rank's K and V go into a staging block; the exchange brings every other rank's block into
-    this rank's own HBM on a communication stream while pass 1 (local keys) runs; then one pass per source rank,
-    nearest first, each as soon as that rank's block has landed, each continuing the previous pass' softmax
-    state (f32 result + log-sum-exp).  Only the first block's transfer has to hide under pass 1; every later one
-    hides under the pass before it.
+    this rank's own HBM on a communication stream while pass 1 (local keys) runs; then passes over the nearest
+    source rank, the next two, the next four, ... (SpLayout.source_groups), each as soon as its blocks have
+    landed, each continuing the previous pass' softmax state (f32 result + log-sum-exp).  Only the first
+    block's transfer has to hide under pass 1; every later one hides under the passes before it.
 
     exchange="ce" (default): the staging block is peer-mapped (torch symmetric memory, multicast off) and the
       other ranks PULL it with plain device-to-device copies that the copy engines carry out over NVLink -- no SM
@@ -193,9 +221,12 @@ class SpAttention:
       call n + 1 every peer has finished pulling call n, and call n + 2 is the next one to write that half).
     exchange="nccl": ncclAllGather of K and of V, then one remote pass over all of it."""
 
-    def __init__(self, seq: int, bh: int, group=None, device=None, zigzag: bool = False, exchange: Optional[str] = None):
+    def __init__(self, seq: int, bh: int, group=None, device=None, zigzag: bool = False, exchange: Optional[str] = None,
+                 grouped: Optional[bool] = None):
         import torch.distributed as dist
         self.dist, self.group = dist, group
+        # remote passes over one, two, four, ... sources (default) or one pass per source (FV_SP_PASSES=per-source)
+        self.grouped = grouped if grouped is not None else os.environ.get("FV_SP_PASSES", "grouped") != "per-source"
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
@@ -304,12 +335,20 @@ class SpAttention:
         segments_fwd(q, mine_k, mine_v, l1, s1, L.run_rows, scale, out=self.o_buf[0], lse_out=self.lse_buf[0], **common)
         if self.exchange == "ce":
             # one pass per source rank as its block lands, each continuing the state of the one before
-            for n, src in enumerate(order):
-                cur.wait_event(arrived[src])
-                ln, st = L.source_segments(src, causal)
-                last = n == len(order) - 1
+            groups = L.source_groups(causal, self.grouped)
+            k_flat = self.k_all.view(-1, self.bh, L.run_rows, d)
+            v_flat = self.v_all.view(-1, self.bh, L.run_rows, d)
+            for n, srcs in enumerate(groups):
+                cur.wait_event(arrived[srcs[-1]])  # (the copies are in stream order: the last one's event covers the group)
+                last = n == len(groups) - 1
                 a, b = n & 1, 1 - (n & 1)
-                segments_fwd(q, self.k_all[src], self.v_all[src], ln, st, L.run_rows, scale,
+                if len(srcs) == 1:
+                    ln, st = L.source_segments(srcs[0], causal)
+                    kk, vv = self.k_all[srcs[0]], self.v_all[srcs[0]]
+                else:
+                    ln, st = L.group_segments(srcs, causal)
+                    kk, vv = k_flat, v_flat
+                segments_fwd(q, kk, vv, ln, st, L.run_rows, scale,
                              out=out if last else self.o_buf[b], lse_out=None if last else self.lse_buf[b],
                              prev_o=self.o_buf[a], prev_lse=self.lse_buf[a], **common)
         else:

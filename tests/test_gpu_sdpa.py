@@ -267,12 +267,13 @@ def test_sequence_parallel_block_causal_rank_by_rank(fvlib, oracle, world, bt, w
     assert_close(to_host_f32(got), oracle.sdpa_rows(q, k, v, block_causal=(bt, win, sink)), f"sp{world} causal bt{bt} w{win} s{sink}")
 
 
+@pytest.mark.parametrize("grouped", [True, False])
 @pytest.mark.parametrize("world,zigzag,mask", [(2, False, None), (4, False, None), (4, True, (130, 0, 0)), (3, True, (64, 2, 1)),
-                                               (8, True, (100, 0, 0)), (4, True, None)])
-def test_sequence_parallel_chained_passes_rank_by_rank(fvlib, oracle, world, zigzag, mask):
+                                               (8, True, (100, 0, 0)), (4, True, None), (8, False, None)])
+def test_sequence_parallel_chained_passes_rank_by_rank(fvlib, oracle, world, zigzag, mask, grouped):
     """The launches of SpAttention.forward with the copy-engine exchange, run rank after rank on one GPU: pass 1
-    over the rank's own runs, then one pass per source rank in SpLayout.source_order, each continuing the
-    previous pass' f32 state -- contiguous shards and the zig-zag split (two runs of query rows per rank), dense
+    over the rank's own runs, then the passes of SpLayout.source_groups (one, two, four ... sources per pass, or one
+    source each), each continuing the previous pass' f32 state -- contiguous shards and the zig-zag split (two runs of query rows per rank), dense
     and block-causal.  Runs a rank does not fetch are poisoned with NaN.  Put back in sequence order the rows
     equal the one-launch kernel and the oracle."""
     from fastvideo_rs_b200 import sdpa, sp
@@ -309,14 +310,20 @@ def test_sequence_parallel_chained_passes_rank_by_rank(fvlib, oracle, world, zig
             lb = [torch.empty((bh, lay.len), dtype=torch.float32, device="cuda") for _ in range(2)]
             sp.segments_fwd(qr, kb[lay.rank], vb[lay.rank], l1, s1, lay.run_rows, scale, out=ob[0], lse_out=lb[0], **common)
             o = None
-            for n, src in enumerate(order):
-                ln, st = lay.source_segments(src, causal)
-                ks, vs = kb[src].clone(), vb[src].clone()
+            groups = lay.source_groups(causal, grouped)
+            assert [s for g in groups for s in g] == order
+            for n, srcs in enumerate(groups):
+                if len(srcs) == 1:
+                    ln, st = lay.source_segments(srcs[0], causal)
+                    ks, vs = kb[srcs[0]].clone(), vb[srcs[0]].clone()
+                else:  # several sources in one pass: segments over the whole gathered buffer
+                    ln, st = lay.group_segments(srcs, causal)
+                    ks, vs = torch.cat(kb).clone(), torch.cat(vb).clone()
                 for run, l in enumerate(ln):
-                    if l == 0:  # not fetched
+                    if l == 0:  # not fetched, or not this pass'
                         ks[run].fill_(float("nan"))
                         vs[run].fill_(float("nan"))
-                last = n == len(order) - 1
+                last = n == len(groups) - 1
                 a, b = n & 1, 1 - (n & 1)
                 o = sp.segments_fwd(qr, ks, vs, ln, st, lay.run_rows, scale, out=None if last else ob[b],
                                     lse_out=None if last else lb[b], prev_o=ob[a], prev_lse=lb[a], **common)

@@ -242,3 +242,28 @@ def test_zigzag_layout_balances_the_causal_work_and_covers_the_sequence():
                             assert got == truth, (seq, world, bc, rank, src, run)
                 lens, starts = lay.pass2_for(bc)
                 assert len(lens) == world * lay.nrun and all(l == 0 for l in lens[rank * lay.nrun:(rank + 1) * lay.nrun])
+
+
+def test_source_groups_cover_the_order_once_and_double():
+    """SpLayout.source_groups: the pull order cut into passes of 1, 2, 4, ... sources (or one each); group_segments
+    leaves exactly the group's visible runs non-empty at their global offsets."""
+    from fastvideo_rs_b200 import sp
+    from fastvideo_rs_b200.sdpa import BlockCausal
+    for world in (2, 3, 4, 8):
+        for zigzag, causal in ((False, None), (True, BlockCausal(100, 0, 0))):
+            for rank in range(world):
+                lay = sp.SpLayout(1001, world, rank, zigzag=zigzag)
+                order = lay.source_order(causal)
+                groups = lay.source_groups(causal, True)
+                assert [s for g in groups for s in g] == order
+                assert [len(g) for g in groups[:-1]] == [2 ** i for i in range(len(groups) - 1)]
+                assert lay.source_groups(causal, False) == [[s] for s in order]
+                need = lay.needed(causal)
+                for g in groups:
+                    lens, starts = lay.group_segments(g, causal)
+                    assert len(lens) == world * lay.nrun
+                    for r in range(world):
+                        for run, (s0, l) in enumerate(lay.runs[r]):
+                            i = r * lay.nrun + run
+                            assert starts[i] == s0
+                            assert lens[i] == (l if (r in g and need.get(r, [False] * lay.nrun)[run]) else 0)
