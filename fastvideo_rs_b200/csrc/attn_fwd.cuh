@@ -582,6 +582,15 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
         const Span row_span = span_of<MASKED>(jb, global_row(jb, qr), global_row(jb, qr));
         RowState rs{neg_inf(), 0.f};
         int seen = 0;
+        if (jb.prev_o && qr < jb.sq) {
+            // A later pass merges the earlier pass' f32 row in its epilogue.  Each thread reads its own row there
+            // (512 bytes, four lines that no other thread shares), one dependent DRAM round trip per 32 columns on
+            // the item's critical path: asked for now, the lines are in L2 by then.
+            const float* pr = jb.prev_o + ((size_t)it.plane * jb.sq + qr) * kD;
+#pragma unroll
+            for (int c = 0; c < 4; c++) asm volatile("prefetch.global.L2 [%0];" ::"l"(pr + 32 * c));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(jb.prev_lse + (size_t)it.plane * jb.sq + qr));
+        }
         KeyWalk<MASKED> walk;
         KeyTile kt;
         while (walk.next(jb, cta_span, kt)) {
