@@ -45,6 +45,7 @@ struct LaunchArgs {
     int out_is_bf16 = 1, planes = 0, sq = 0, nseg = 1;
     const int *seg_len = nullptr, *seg_start = nullptr;
     int seg_rows = 0;
+    int kv_plane_rows = 0;  // rows between two planes of k / v when they are windows of longer planes (0: seg_rows)
     float scale = 0.f;
     int mask_mode = FV_MASK_NONE, block_tokens = 0, window = 0, sink = 0, q_row0 = 0;
     float* lse_out = nullptr;
@@ -133,8 +134,11 @@ static int launch(cudaStream_t stream, const LaunchArgs& a) {
         const uint64_t sqb[3] = {256, (uint64_t)a.sq * 256, (uint64_t)a.sq * 256 * qplanes};
         rc = fvrt::encode_map4_cached(&mq, a.q, dq, sqb, 128);
         if (rc != FV_RAN) return rc;
+        // (a window of a longer plane: the map's row extent stays the window, so rows past it read as zeros and
+        // nothing beyond the last plane's window is touched; only the plane stride is the longer plane's)
+        const uint64_t plane_rows = (uint64_t)(a.kv_plane_rows > 0 ? a.kv_plane_rows : a.seg_rows);
         const uint64_t dk[4] = {128, (uint64_t)a.seg_rows, (uint64_t)a.planes, (uint64_t)a.nseg};
-        const uint64_t skb[3] = {256, (uint64_t)a.seg_rows * 256, (uint64_t)a.seg_rows * 256 * a.planes};
+        const uint64_t skb[3] = {256, plane_rows * 256, plane_rows * 256 * a.planes};
         rc = fvrt::encode_map4_cached(&mk, a.k, dk, skb, 128);
         if (rc != FV_RAN) return rc;
         rc = fvrt::encode_map4_cached(&mv, a.v, dk, skb, 128);
@@ -408,6 +412,28 @@ extern "C" int fv_sdpa_dense_bf16(void* stream, const void* q, const void* k, co
     if (d != 128 || bh <= 0 || sq <= 0 || sk <= 0) return FV_DECLINED;
     if (sq > 0x3fffffff || sk > 0x3fffffff) return FV_DECLINED;
     return dense_call(stream, q, k, v, out, out_is_bf16, bh, sq, sk, scale, mask_mode, block_tokens, window, sink, q_row0, 0);
+}
+
+extern "C" int fv_sdpa_window_bf16(void* stream, const void* q, const void* k_cache, const void* v_cache, void* out,
+                                   int out_is_bf16, int bh, int sq, int cache_rows, int window_start, int window_len, int d,
+                                   float scale, int out_heads) {
+    fvrt::clear_error();
+    if (d != 128 || bh <= 0 || sq <= 0 || window_len <= 0) return FV_DECLINED;
+    if (sq > 0x3fffffff || cache_rows > 0x3fffffff) return FV_DECLINED;
+    if (window_start < 0 || (long long)window_start + window_len > cache_rows)
+        return fvrt::fail(FV_ERR_INVALID, "sdpa window: rows [%d, %d) outside a cache of %d rows", window_start,
+                          window_start + window_len, cache_rows);
+    if (out_heads < 0 || (out_heads > 0 && bh % out_heads != 0)) return fvrt::fail(FV_ERR_INVALID, "sdpa window: out_heads %d", out_heads);
+    if (!k_cache || !v_cache) return fvrt::fail(FV_ERR_INVALID, "sdpa: null operand");
+    const int len = window_len, start = 0;
+    fvattn::LaunchArgs a;
+    a.q = q;
+    a.k = static_cast<const unsigned short*>(k_cache) + (size_t)window_start * 128;
+    a.v = static_cast<const unsigned short*>(v_cache) + (size_t)window_start * 128;
+    a.out = out; a.out_is_bf16 = out_is_bf16; a.planes = bh; a.sq = sq;
+    a.nseg = 1; a.seg_len = &len; a.seg_start = &start; a.seg_rows = window_len; a.kv_plane_rows = cache_rows; a.scale = scale;
+    a.out_heads = out_heads;
+    return fvattn::launch((cudaStream_t)stream, a);
 }
 
 extern "C" int fv_sdpa_dense_merged_bf16(void* stream, const void* q, const void* k, const void* v, void* out,

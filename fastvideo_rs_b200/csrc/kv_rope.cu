@@ -120,3 +120,64 @@ extern "C" int fv_wan_rope_bhsd(void* stream, const void* src, int src_is_bf16, 
     FV_CUDA(cudaGetLastError());
     return FV_RAN;
 }
+
+// ---- the cache's pointer arithmetic and its roll ----------------------------------------------------------
+// KvSpec::plan (crates/fastvideo-cudarc/src/wan/causal.rs:289-336): where a block of n tokens that starts at
+// token current_start of the rollout goes in a cache whose state is (global_end, local_end_prev).
+extern "C" int fv_kv_plan(const fv_kv_spec* spec, long long global_end, long long local_end_prev, long long current_start,
+                          long long n, fv_kv_move* out) {
+    fvrt::clear_error();
+    if (!spec || !out) return fvrt::fail(FV_ERR_INVALID, "kv plan: null argument");
+    if (global_end < 0 || local_end_prev < 0 || current_start < 0 || n < 0 || spec->capacity < 0 || spec->max_attention < 0)
+        return fvrt::fail(FV_ERR_INVALID, "kv plan: negative argument");
+    const long long current_end = current_start + n;
+    if (!spec->rolling && current_end > spec->max_attention)
+        return fvrt::fail(FV_ERR_INVALID,
+                          "causal Wan local_attn_size=-1 keeps a %lld-frame KV window; got current_end=%lld tokens with "
+                          "frame_seqlen=%d (set local_attn_size for longer rollouts)",
+                          (long long)spec->max_attention / (spec->frame_tokens > 0 ? spec->frame_tokens : 1), current_end,
+                          spec->frame_tokens);
+    if (current_end < global_end && current_end + local_end_prev < global_end)
+        return fvrt::fail(FV_ERR_INVALID, "causal kv: block before the cache start");
+    const long long advance = current_end > global_end ? current_end - global_end : 0;
+    const long long evicted =
+        (spec->rolling && current_end > global_end && n + local_end_prev > spec->capacity) ? n + local_end_prev - spec->capacity : 0;
+    const long long back = global_end > current_end ? global_end - current_end : 0;
+    long long local_end = local_end_prev + advance;
+    if (local_end < back || local_end - back < evicted) return fvrt::fail(FV_ERR_INVALID, "causal kv: pointer underflow");
+    local_end = local_end - back - evicted;
+    if (local_end < n) return fvrt::fail(FV_ERR_INVALID, "causal kv: block longer than the cache");
+    const long long cap = spec->capacity > n ? spec->capacity : n;
+    if (local_end > cap) return fvrt::fail(FV_ERR_INVALID, "causal kv: write end %lld past the cache (%d tokens)", local_end, spec->capacity);
+    out->evicted = evicted;
+    out->local_start = local_end - n;
+    out->local_end = local_end;
+    out->window_start = local_end > spec->max_attention ? local_end - spec->max_attention : 0;
+    return FV_RAN;
+}
+
+// The roll of a full cache (causal.rs:560-585 / update_static): rows [sink + evicted, local_end_prev) of every plane
+// move down to row sink.  Source and destination overlap when more rows move than are evicted, so the move goes
+// in chunks no longer than the shift (shift_tokens_down, causal.rs:236-249), each one strided 2-D copy over all
+// planes on the caller's stream.
+extern "C" int fv_kv_roll(void* stream, void* cache, int elem_bytes, int planes, int cache_rows, int sink, int evicted,
+                          int local_end_prev) {
+    fvrt::clear_error();
+    if (planes <= 0 || evicted <= 0) return FV_DECLINED;
+    if (!cache) return fvrt::fail(FV_ERR_INVALID, "kv roll: null cache");
+    if ((elem_bytes != 2 && elem_bytes != 4) || sink < 0 || local_end_prev > cache_rows || sink + evicted > local_end_prev)
+        return fvrt::fail(FV_ERR_INVALID, "kv roll: sink %d + evicted %d against %d cached rows of %d", sink, evicted, local_end_prev,
+                          cache_rows);
+    const size_t row = (size_t)fvkv::kD * elem_bytes, pitch = (size_t)cache_rows * row;
+    unsigned char* base = static_cast<unsigned char*>(cache);
+    int from = sink + evicted, to = sink, left = local_end_prev - from;
+    while (left > 0) {
+        const int n = left < evicted ? left : evicted;
+        FV_CUDA(cudaMemcpy2DAsync(base + (size_t)to * row, pitch, base + (size_t)from * row, pitch, (size_t)n * row, planes,
+                                  cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+        from += n;
+        to += n;
+        left -= n;
+    }
+    return FV_RAN;
+}

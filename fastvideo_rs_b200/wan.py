@@ -5,7 +5,7 @@ between the QKV projection and the output projection."""
 from __future__ import annotations
 
 import ctypes
-from typing import Optional, Tuple
+from typing import NamedTuple, Optional, Tuple
 
 import numpy as np
 import torch
@@ -173,6 +173,158 @@ def rope_bhsd(src: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, dst: torc
                                          int(dst.dtype == torch.bfloat16), dst.shape[2], int(dst_row0))
     _lib.check(rc, "rope_bhsd")
     return dst
+
+
+class _KvSpecC(ctypes.Structure):
+    _fields_ = [("frame_tokens", ctypes.c_int), ("capacity", ctypes.c_int), ("sink", ctypes.c_int),
+                ("max_attention", ctypes.c_int), ("rolling", ctypes.c_int)]
+
+
+class _KvMoveC(ctypes.Structure):
+    _fields_ = [("evicted", ctypes.c_longlong), ("local_start", ctypes.c_longlong), ("local_end", ctypes.c_longlong),
+                ("window_start", ctypes.c_longlong)]
+
+
+class KvMove(NamedTuple):
+    """Where the cache pointers moved for one write (KvMove, wan/causal.rs:276-287)."""
+    evicted: int
+    local_start: int
+    local_end: int
+    window_start: int
+
+
+class KvSpec:
+    """Token geometry of one causal K/V cache (KvSpec, wan/causal.rs:38-147): tokens per latent frame, rows of a
+    cache plane, rows kept at the head when it rolls, keys a block reads back from its end, and whether it rolls
+    (local_attn_size given) or refuses clips longer than its window."""
+
+    def __init__(self, frame_tokens: int, capacity: int, sink: int, max_attention: int, rolling: bool):
+        self.frame_tokens, self.capacity, self.sink = int(frame_tokens), int(capacity), int(sink)
+        self.max_attention, self.rolling = int(max_attention), bool(rolling)
+
+    @staticmethod
+    def rolling_window(frame_tokens: int, local_attn_frames: int, sink_frames: int) -> "KvSpec":
+        """KvSpec::rolling (wan/causal.rs:110-133): a cache of local_attn_frames frames that keeps the first
+        sink_frames frames when it rolls."""
+        if local_attn_frames == 0 or sink_frames >= local_attn_frames:
+            raise ValueError(f"causal kv: sink {sink_frames} frames must be below the window ({local_attn_frames} frames)")
+        n = local_attn_frames * frame_tokens
+        return KvSpec(frame_tokens, n, sink_frames * frame_tokens, n, True)
+
+    @staticmethod
+    def global_window(frame_tokens: int, frames: int = 21, sink_frames: int = 0) -> "KvSpec":
+        """local_attn_size == -1 (KvSpec::for_config, wan/causal.rs:80-107): sliding_window_num_frames frames, no roll."""
+        n = frames * frame_tokens
+        return KvSpec(frame_tokens, n, sink_frames * frame_tokens, n, False)
+
+    def window_frames(self) -> int:
+        return self.max_attention // max(self.frame_tokens, 1)
+
+    def sink_target(self, end_frame: int) -> int:
+        """First frame the sink keys should sit at once the write that ends at end_frame is done (wan/causal.rs:136-138)."""
+        return max(end_frame - self.window_frames(), 0)
+
+    def plan(self, global_end: int, local_end_prev: int, current_start: int, n: int) -> KvMove:
+        """KvSpec::plan (wan/causal.rs:289-336) through the library (host arithmetic, no device needed)."""
+        c = _KvSpecC(self.frame_tokens, self.capacity, self.sink, self.max_attention, int(self.rolling))
+        mv = _KvMoveC()
+        rc = _lib.lib().fv_kv_plan(ctypes.byref(c), ctypes.c_longlong(global_end), ctypes.c_longlong(local_end_prev),
+                                   ctypes.c_longlong(current_start), ctypes.c_longlong(n), ctypes.byref(mv))
+        _lib.check(rc, "kv plan")
+        return KvMove(mv.evicted, mv.local_start, mv.local_end, mv.window_start)
+
+
+class CausalKvCache:
+    """One layer's causal K/V cache as persistent buffers (CausalKvCache in static mode, wan/causal.rs:338-730):
+    k, v [batch, heads, capacity, 128] bf16 written in place, the pointers (global_end, local_end) on the host.
+    A block is planned (KvSpec.plan), the cache rolled past its sink when full (fv_kv_roll), the block written at
+    [local_start, local_end) -- by `update` from BHSD tensors like the reference, or by `prep` straight out of the
+    prologue kernel -- and its queries attend to rows [window_start, local_end) in place (`attend`,
+    Plan::kv_window)."""
+
+    def __init__(self, spec: KvSpec, batch: int, heads: int, device="cuda"):
+        self.spec, self.batch, self.heads = spec, batch, heads
+        self.k = torch.zeros((batch, heads, spec.capacity, 128), dtype=torch.bfloat16, device=device)
+        self.v = torch.zeros_like(self.k)
+        self.global_end = self.local_end = 0
+        self.last: Optional[KvMove] = None
+        self.raw_sink: Optional[torch.Tensor] = None  # KvRope::RebasedSink: the sink keys without RoPE (f32), taken once
+        self.sink_at = 0                              # first frame the cached sink keys are roped at now
+
+    def __len__(self) -> int:
+        return self.local_end
+
+    def reset(self) -> None:
+        self.global_end = self.local_end = 0
+        self.last = None
+        self.raw_sink, self.sink_at = None, 0
+
+    def rebase_sink(self, target: int, orig, new) -> None:
+        """CausalKvCache::rebase_sink (wan/causal.rs:734-812): re-rope the sink keys to start at frame `target`
+        (KvSpec.sink_target).  orig = (cos, sin) tables of the sink's own frames 0 .. sink (to take the un-roped copy
+        the first time, by rotating back), new = those of frames target .. target + sink ([sink_tokens, 128] f32
+        each).  Two launches of the BHSD rope kernel, the second writing the cache head in place; a no-op when the
+        sink is already there."""
+        sink = self.spec.sink
+        if sink == 0 or self.local_end < sink or self.sink_at == target:
+            return
+        if self.raw_sink is None:
+            self.raw_sink = torch.empty((self.batch, self.heads, sink, 128), dtype=torch.float32, device=self.k.device)
+            rope_bhsd(self.k, orig[0], orig[1], self.raw_sink, negate_sin=True)
+        rope_bhsd(self.raw_sink, new[0], new[1], self.k)
+        self.sink_at = target
+
+    def _advance(self, current_start: int, n: int) -> KvMove:
+        mv = self.spec.plan(self.global_end, self.local_end, current_start, n)
+        if mv.evicted > 0:
+            for t in (self.k, self.v):
+                with torch.cuda.device(t.device):
+                    rc = _lib.lib().fv_kv_roll(_stream_ptr(), ctypes.c_void_p(t.data_ptr()), 2, self.batch * self.heads,
+                                               self.spec.capacity, self.spec.sink, int(mv.evicted), self.local_end)
+                _lib.check(rc, "kv roll")
+        return mv
+
+    def _commit(self, mv: KvMove, current_start: int, n: int) -> None:
+        self.global_end, self.local_end, self.last = current_start + n, mv.local_end, mv
+
+    def update(self, k: torch.Tensor, v: torch.Tensor, current_start: int):
+        """CausalKvCache::update (wan/causal.rs:541-628): write a block's roped K and V [batch, heads, n, 128] at
+        rollout position current_start; returns the (k, v) windows its queries read, as views of the cache."""
+        n = k.shape[2]
+        mv = self._advance(current_start, n)
+        self.k[:, :, mv.local_start:mv.local_end].copy_(k)
+        self.v[:, :, mv.local_start:mv.local_end].copy_(v)
+        self._commit(mv, current_start, n)
+        return self.k[:, :, mv.window_start:mv.local_end], self.v[:, :, mv.window_start:mv.local_end]
+
+    def prep(self, proj: torch.Tensor, wq, wk, cos, sin, current_start: int, eps: float = 1e-6) -> torch.Tensor:
+        """The block's fused QKV projection [batch, n, 3 * dim] through the prologue kernel with K and V landing in
+        the cache rows of the block (no copy launches); returns q [batch, heads, n, 128].  cos / sin: the table rows
+        of the block's own frames."""
+        n = proj.shape[1]
+        mv = self._advance(current_start, n)
+        q, _, _ = qk_prep(proj, wq, wk, cos, sin, self.heads, eps=eps, cache=(self.k, self.v, mv.local_start))
+        self._commit(mv, current_start, n)
+        return q
+
+    def attend(self, q: torch.Tensor, scale: Optional[float] = None, merged: bool = False) -> torch.Tensor:
+        """Plan::kv_window over the cache (rt/sdpa.rs:122-133; wan/transformer.rs:290-313): the block's queries
+        [batch, heads, n, 128] against rows [window_start, local_end) of the cache, read in place."""
+        if self.last is None:
+            raise ValueError("attend: nothing has been written to the cache")
+        if q.dtype != torch.bfloat16 or not q.is_cuda or not q.is_contiguous() or q.dim() != 4 or q.shape[:2] != (self.batch, self.heads):
+            raise ValueError("attend: q must be a contiguous CUDA bf16 [batch, heads, n, 128] tensor")
+        b, h, n, d = q.shape
+        scale = float(scale) if scale is not None else 1.0 / d ** 0.5
+        out = torch.empty((b, n, h * d) if merged else (b, h, n, d), dtype=torch.bfloat16, device=q.device)
+        ws, we = self.last.window_start, self.last.local_end
+        with torch.cuda.device(q.device):
+            rc = _lib.lib().fv_sdpa_window_bf16(_stream_ptr(), ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(self.k.data_ptr()),
+                                                ctypes.c_void_p(self.v.data_ptr()), ctypes.c_void_p(out.data_ptr()), 1, b * h, n,
+                                                self.spec.capacity, int(ws), int(we - ws), d, ctypes.c_float(scale),
+                                                h if merged else 0)
+        _lib.check(rc, "sdpa window")
+        return out
 
 
 def ln_adaln_e(x: torch.Tensor, e: torch.Tensor, scale_slot: int, shift_slot: int, eps: float = 1e-6) -> torch.Tensor:

@@ -227,6 +227,35 @@ FV_API int fv_wan_rope_bhsd(void* stream, const void* src, int src_is_bf16, int 
                             const float* cosv, const float* sinv, int negate_sin, int planes, int n, void* dst,
                             int dst_is_bf16, int dst_plane_rows, int dst_row0);
 
+/* The cache's host arithmetic and its roll.
+ * fv_kv_plan is KvSpec::plan (crates/fastvideo-cudarc/src/wan/causal.rs:289-336): for a block of n tokens that starts
+ * at token current_start of the rollout and a cache in state (global_end, local_end_prev) it gives the rows the
+ * block is written to [local_start, local_end), the rows dropped after the sink first (evicted) and the first row
+ * the block's queries read (window_start); the reference's errors (a global window asked for more frames than it
+ * keeps, a block before the cache start, a write past the cache) are FV_ERR_INVALID with the reference's text.
+ * fv_kv_roll moves rows [sink + evicted, local_end_prev) of every plane of a [planes, cache_rows, 128] cache
+ * (elem_bytes 2 or 4) down to row sink, in chunks that do not overlap (shift_tokens_down, causal.rs:236-249).
+ * fv_sdpa_window_bf16 is Plan::kv_window over such a cache (rt/sdpa.rs:122-133,300-326; wan/transformer.rs:290-313):
+ * unmasked attention of q [bh, sq, 128] over rows [window_start, window_start + window_len) of k_cache / v_cache
+ * [bh, cache_rows, 128] bf16, read in place (no narrow + copy); out_heads as in fv_sdpa_dense_merged_bf16 (0: BHSD). */
+typedef struct fv_kv_spec {
+    int frame_tokens;   /* tokens per latent frame */
+    int capacity;       /* rows of a cache plane */
+    int sink;           /* rows kept at the head when the cache rolls */
+    int max_attention;  /* keys a block reads, back from its end */
+    int rolling;        /* 1: local_attn_size given, the cache rolls; 0: a clip longer than the window is an error */
+} fv_kv_spec;
+typedef struct fv_kv_move {
+    long long evicted, local_start, local_end, window_start;
+} fv_kv_move;
+FV_API int fv_kv_plan(const fv_kv_spec* spec, long long global_end, long long local_end_prev, long long current_start,
+                      long long n, fv_kv_move* out);
+FV_API int fv_kv_roll(void* stream, void* cache, int elem_bytes, int planes, int cache_rows, int sink, int evicted,
+                      int local_end_prev);
+FV_API int fv_sdpa_window_bf16(void* stream, const void* q, const void* k_cache, const void* v_cache, void* out,
+                               int out_is_bf16, int bh, int sq, int cache_rows, int window_start, int window_len, int d,
+                               float scale, int out_heads);
+
 /* ---- operand rounding for f32-stored activations ------------------------------------------------
  * The reference rounds q, k, v to bf16 before its attention kernels under bf16 activations and rounds the
  * result again (act16_operands and the tail of dense, crates/fastvideo-cudarc/src/rt/sdpa.rs:167-181,184-214:

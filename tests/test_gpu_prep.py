@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from _util import to_dev_bf16, to_host_f32
+from _util import assert_close, to_dev_bf16, to_host_f32
 
 pytestmark = pytest.mark.gpu
 
@@ -183,3 +183,81 @@ def test_rope_bhsd_rebases_a_sink(fvlib, oracle):
     assert np.array_equal(to_host_f32(mid).reshape(b * h, cap, 128)[:, 200:200 + sink], want_mid)
     with pytest.raises(Exception):
         wan.rope_bhsd(kc, tcn, tsn, raw, src_row0=cap - sink + 1)
+    # the same through the cache object: un-roped copy taken once, sink re-roped in place, second call a no-op
+    cache = wan.CausalKvCache(wan.KvSpec(78, cap, sink, cap, True), b, h)
+    cache.k.copy_(to_dev_bf16(x).view(b, h, cap, 128))
+    cache.local_end = cap
+    cache.rebase_sink(3, (tco, tso), (tcn, tsn))
+    assert np.array_equal(to_host_f32(cache.k).reshape(b * h, cap, 128), got)
+    before = cache.k.clone()
+    cache.rebase_sink(3, (tco, tso), (tcn, tsn))
+    assert torch.equal(cache.k, before) and cache.sink_at == 3
+
+
+def test_kv_cache_update_keeps_prefix_and_window(fvlib):
+    """update_keeps_prefix_and_window of the reference (wan/causal.rs:1113-1155) on the device cache: blocks of four
+    tokens into a rolling cache of eight rows with a two-row sink; every row carries one value."""
+    from fastvideo_rs_b200 import wan
+    cache = wan.CausalKvCache(wan.KvSpec(2, 8, 2, 8, True), 1, 1)
+
+    def blk(base):
+        return (base + torch.arange(4, dtype=torch.float32, device="cuda")).view(1, 1, 4, 1).expand(1, 1, 4, 128).contiguous().bfloat16()
+
+    def rows(t):
+        assert (t == t[..., :1]).all()
+        return t[0, 0, :, 0].float().tolist()
+
+    k, _ = cache.update(blk(0.0), blk(0.0), 0)
+    assert rows(k) == [0.0, 1.0, 2.0, 3.0]
+    k, _ = cache.update(blk(10.0), blk(10.0), 0)       # the same block again (next step): overwritten
+    assert rows(k) == [10.0, 11.0, 12.0, 13.0]
+    k, _ = cache.update(blk(20.0), blk(20.0), 4)
+    assert k.shape[2] == 8
+    k, v = cache.update(blk(30.0), blk(30.0), 8)       # third block: 4 evicted after the 2-row sink
+    assert rows(k) == [10.0, 11.0, 22.0, 23.0, 30.0, 31.0, 32.0, 33.0] and rows(v) == rows(k)
+    assert len(cache) == 8
+    k, _ = cache.update(blk(40.0), blk(40.0), 12)      # fourth block: the roll moves 2 rows down by 4
+    assert rows(k) == [10.0, 11.0, 32.0, 33.0, 40.0, 41.0, 42.0, 43.0]
+    cache.reset()
+    assert len(cache) == 0
+
+
+def test_kv_cache_roll_with_overlap_prep_and_window_attention(fvlib, oracle):
+    """A roll whose source and destination overlap (more rows move than are evicted), blocks written by the prologue
+    kernel, and the block's queries attending to the window in place -- against the oracle over the same rows."""
+    from fastvideo_rs_b200 import sdpa, wan
+    batch, heads, ft, n = 1, 3, 26, 52          # 2 frames of 26 tokens per block
+    grid = (2, 2, 13)
+    dim = heads * 128
+    spec = wan.KvSpec.rolling_window(ft, 7, 1)  # 182 rows, sink 26: the third roll moves 104 rows down by 52
+    cache = wan.CausalKvCache(spec, batch, heads)
+    w = np.ones(dim, np.float32)
+    tw = torch.from_numpy(w).cuda()
+    host_k, host_v = [], []                     # the cache as the host would hold it: lists of [heads, rows, 128]
+    for b in range(5):
+        proj = oracle.bf16_round(oracle.seeded_normal(37, b, (batch, n, 3 * dim)))
+        cos, sin = oracle.wan_rope(*grid, start_frame=2 * b)
+        tc, ts = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+        q = cache.prep(to_dev_bf16(proj), tw, tw, tc, ts, b * n)
+        out = cache.attend(q)
+        assert sdpa.device_status() == 0
+        kq = oracle.bf16_round(oracle.qk_norm_rope_bhsd(proj, w, cos, sin, batch, n, heads, 128, 3 * dim, 0))
+        kk = oracle.bf16_round(oracle.qk_norm_rope_bhsd(proj, w, cos, sin, batch, n, heads, 128, 3 * dim, dim))
+        vv = oracle.split_heads_bhsd(proj, batch, n, heads, 128, 3 * dim, 2 * dim)
+        if sum(x.shape[1] for x in host_k) + n > spec.capacity:   # roll: the sink stays, the oldest rows after it go
+            allk, allv = np.concatenate(host_k, 1), np.concatenate(host_v, 1)
+            ev = allk.shape[1] + n - spec.capacity
+            host_k = [np.concatenate([allk[:, :spec.sink], allk[:, spec.sink + ev:]], 1)]
+            host_v = [np.concatenate([allv[:, :spec.sink], allv[:, spec.sink + ev:]], 1)]
+        host_k.append(kk)
+        host_v.append(vv)
+        allk, allv = np.concatenate(host_k, 1), np.concatenate(host_v, 1)
+        L = allk.shape[1]
+        assert len(cache) == L
+        got_k = to_host_f32(cache.k[0, :, :L])
+        assert np.mean(got_k != allk) < 2e-3     # (one rounding of the prologue, ties aside)
+        assert np.array_equal(to_host_f32(cache.v[0, :, :L]), allv)
+        want = oracle.sdpa_rows(kq, to_host_f32(cache.k[0, :, :L]), allv)
+        assert_close(to_host_f32(out).reshape(heads, n, 128), want, f"window attention, block {b}")
+    merged = cache.attend(q, merged=True)
+    assert torch.equal(merged, out.permute(0, 2, 1, 3).reshape(batch, n, dim))
