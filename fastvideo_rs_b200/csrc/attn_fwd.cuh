@@ -480,7 +480,7 @@ struct RowState {
 //   late_only: the early part of P is already with the issuer (stored against the old reference);
 //   its product must have finished before O is touched -- the caller has waited for pv_early.
 //   have_o: O holds products of this item (earlier tiles, or this tile's early part).
-__device__ __noinline__ void careful_tile(uint32_t tS, uint32_t tO, uint32_t bt, Cols cols, float sl2, bool late_only,
+static __device__ __noinline__ void careful_tile(uint32_t tS, uint32_t tO, uint32_t bt, Cols cols, float sl2, bool late_only,
                                           bool have_o, int lane, RowState* rs) {
     float m = rs->m, l = rs->l;
     const int first = late_only ? kEarlyChunks : 0;

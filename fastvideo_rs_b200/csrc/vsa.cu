@@ -277,372 +277,7 @@ __global__ void __launch_bounds__(256) vsa_topk_warp_kernel(const float* __restr
 }
 
 // ------------------------------------------------------------------ 5. fine attention + combine
-// CTA = two query tiles (128 rows) of one head, 6 warps: 0-3 softmax (thread = TMEM lane = row;
-// rows 0-63 are tile 2p, rows 64-127 tile 2p+1), 4 list builder + TMA producer, 5 MMA issuer.
-// The CTA walks the ascending union of the two tiles' selections, one 64-key tile per step; an
-// entry word says which of the two query tiles selected it (the other one's rows get P = 0) and how
-// many of its 64 slots are real keys.  TMEM (256 columns, two CTAs per SM): two S buffers at 0 and 64 (64
-// columns each; the bf16 P of a step overwrites columns 0-31 of its buffer), O at 128 (128 columns).  Q.K^T runs two
-// steps ahead of P.V, so the softmax of step j+1 starts as soon as that of step j ends.
-constexpr int kFineThreads = 192;
-constexpr int kFineNS = 4;
-constexpr uint32_t kKvTileB = 16384;   // 64 x 128 bf16: two 8 KB panels
-constexpr uint32_t kKvPanelB = 8192;
-constexpr uint32_t kQTileB = 32768;    // 128 x 128 bf16: two 16 KB panels
-constexpr uint32_t kQPanelB = 16384;
-
-struct FineParams {
-    const uint32_t* selected;     // [bh, nt, topk] ascending
-    const uint32_t* block_sizes;  // [nt]
-    const int32_t* slot_src;      // [nt*64]
-    const float* coarse;          // [bh, nt, 128]
-    const __nv_bfloat16* gate;    // [bh, seq, 128] or null (gate of one)
-    void* out;                    // [bh, seq, 128]
-    int* status;
-    int out_is_bf16;
-    int bh, nt, topk, seq;
-    float sl2;
-    int list_cap;
-};
-
-__global__ void __launch_bounds__(kFineThreads, 2)
-fv_vsa_fine_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
-                   const __grid_constant__ CUtensorMap tv, const __grid_constant__ FineParams p) {
-#if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL)
-    using namespace fvp;
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
-    const uint32_t raw = smem_u32(smem_raw);
-    const uint32_t base = (raw + 1023u) & ~1023u;
-    const uint32_t sQ = base;
-    const uint32_t ring = base + kQTileB;
-    const uint32_t bars = ring + kFineNS * kKvTileB;
-    const uint32_t b_q = bars;
-    const uint32_t b_full = b_q + 8;
-    const uint32_t b_empty = b_full + 8 * kFineNS;
-    const uint32_t b_s = b_empty + 8 * kFineNS;  // [2]: S buffer ready
-    const uint32_t b_p = b_s + 16;               // [2]: P stored in that buffer
-    const uint32_t b_od = b_p + 16;              // one phase per P.V
-    const uint32_t b_o = b_od + 8;               // the last P.V
-    const uint32_t b_drain = b_o + 8;
-    const uint32_t tslot = b_drain + 8;
-    const uint32_t aflag = tslot + 4;
-    const uint32_t nent_a = aflag + 4;
-    const uint32_t list_a = bars + 256;
-    volatile uint32_t* tslot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tslot - raw));
-    volatile int* abort_ptr = reinterpret_cast<volatile int*>(smem_raw + (aflag - raw));
-    volatile int* nent_ptr = reinterpret_cast<volatile int*>(smem_raw + (nent_a - raw));
-    volatile uint32_t* list = reinterpret_cast<volatile uint32_t*>(smem_raw + (list_a - raw));
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int npair = (p.nt + 1) / 2;
-    const int pair = (int)(blockIdx.x % (unsigned)npair), bh = (int)(blockIdx.x / (unsigned)npair);
-    const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
-    const float NEG = __int_as_float(0xff800000);
-
-    if (tid == 0) {
-        mbar_init(b_q, 1);
-        for (int i = 0; i < kFineNS; i++) {
-            mbar_init(b_full + 8 * i, 1);
-            mbar_init(b_empty + 8 * i, 1);
-        }
-        for (int i = 0; i < 2; i++) {
-            mbar_init(b_s + 8 * i, 1);
-            mbar_init(b_p + 8 * i, 128);
-        }
-        mbar_init(b_od, 1);
-        mbar_init(b_o, 1);
-        mbar_init(b_drain, 1);
-        *abort_ptr = (*(volatile int*)p.status != FV_ST_OK) ? 1 : 0;
-        mbar_init_fence();
-    }
-    __syncthreads();
-    if (*abort_ptr) return;  // CTA-uniform
-    if (warp == 5) tmem_alloc(tslot, 256);
-    if (warp == 4) {
-        if (lane == 0) {
-            tma_prefetch_desc(&tq);
-            mbar_expect_tx(b_q, kQTileB);
-            tma_load4(sQ, &tq, b_q, 0, qt0 * TE, bh, 0);
-            tma_load4(sQ + kQPanelB, &tq, b_q, 64, qt0 * TE, bh, 0);
-        }
-        // ---- the ascending union of the two selections, with visibility bits (27: tile qt0, 28: tile qt1)
-        const uint32_t* la = p.selected + ((size_t)bh * p.nt + qt0) * p.topk;
-        const uint32_t* lb = p.selected + ((size_t)bh * p.nt + qt1) * p.topk;
-        const int na = p.topk, nb = qt1 < p.nt ? p.topk : 0;
-        // both selections are staged in shared memory behind the union area, then merged by one lane
-        volatile uint32_t* sa = list + p.list_cap;
-        volatile uint32_t* sb = sa + p.topk;
-        for (int i = lane; i < na; i += 32) sa[i] = la[i];
-        for (int i = lane; i < nb; i += 32) sb[i] = lb[i];
-        __syncwarp();
-        if (lane == 0) {
-            int i = 0, j = 0, n = 0;
-            while ((i < na || j < nb) && n < p.list_cap) {
-                const uint32_t a = i < na ? sa[i] : 0xffffffffu, b = j < nb ? sb[j] : 0xffffffffu;
-                uint32_t e;
-                if (a < b) { e = a | (1u << 27); i++; }
-                else if (b < a) { e = b | (2u << 27); j++; }
-                else { e = a | (3u << 27); i++; j++; }
-                list[n++] = e;
-            }
-            *nent_ptr = n;
-        }
-        __syncwarp();
-        const int n = *nent_ptr;
-        for (int i = lane; i < n; i += 32) {
-            const uint32_t e = list[i];
-            list[i] = e | (min(p.block_sizes[e & 0xFFFFFu], 64u) << 20);
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tbase = *tslot_ptr;
-    const int nent = *nent_ptr;
-
-    if (warp < 4) {
-        // ------------------------------------------------------------ softmax
-        WaitCtl ctl{abort_ptr, p.status, 13};
-        const int row = warp * 32 + lane, half = row >> 6;
-        const uint32_t tl = tbase + ((uint32_t)(warp * 32) << 16);
-        const uint32_t tO = tl + 128u;
-        const float sl2 = p.sl2;
-        float m = NEG, l = 0.f;
-        bool ok = true;
-#pragma unroll 1
-        for (int j = 0; j < nent && ok; j++) {
-            const uint32_t e = list[j];
-            const int valid = (int)((e >> 20) & 127u);
-            const bool vis = ((e >> (27 + half)) & 1u) != 0u;  // warp-uniform: a warp lies inside one half
-            const int bsel = j & 1;
-            const uint32_t tS = tl + 64u * bsel, tP = tS;
-            if (!__all_sync(0xffffffffu, mbar_wait(b_s + 8 * bsel, (j >> 1) & 1, ctl))) { ok = false; break; }
-            tc_fence_after();
-            uint32_t pw[32];
-            if (vis) {
-                uint32_t u[64];
-                {
-                    uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&u[0]);
-                    uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&u[32]);
-                    tmem_ld32_issue(tS, lo);
-                    tmem_ld32_issue(tS + 32u, hi);
-                    tmem_ld_wait();
-                    tmem_pin(u);
-                }
-                if (valid < TE) {
-#pragma unroll
-                    for (int c = 0; c < 64; c++) u[c] = c < valid ? u[c] : __float_as_uint(NEG);
-                }
-                float x0 = __uint_as_float(u[0]), x1 = __uint_as_float(u[1]);
-#pragma unroll
-                for (int c = 2; c < 64; c += 2) {
-                    x0 = fmaxf(x0, __uint_as_float(u[c]));
-                    x1 = fmaxf(x1, __uint_as_float(u[c + 1]));
-                }
-                const float tm2 = fmaxf(x0, x1) * sl2;
-                const bool grow = tm2 > m + 8.0f;
-                float a = 1.f;
-                if (grow) {
-                    a = ex2(m - tm2);
-                    m = tm2;
-                }
-                const float off = (m == NEG) ? 0.f : m;
-                // S_j done only implies PV_{j-2} done (Q.K^T runs two steps ahead): wait for PV_{j-1} before touching O
-                if (j > 0 && __any_sync(0xffffffffu, grow)) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(b_od, (j - 1) & 1, ctl))) { ok = false; break; }
-                    tc_fence_after();
-#pragma unroll 1
-                    for (int q = 0; q < 4; q++) {
-                        uint32_t o[32];
-                        tmem_ld32_issue(tO + 32u * q, o);
-                        tmem_ld_wait();
-                        tmem_pin(o);
-#pragma unroll
-                        for (int c = 0; c < 32; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * a);
-                        tmem_st32(tO + 32u * q, o);
-                    }
-                }
-                float y0 = 0.f, y1 = 0.f;
-#pragma unroll
-                for (int w = 0; w < 32; w++) {
-                    const float p0 = ex2(fmaf(__uint_as_float(u[2 * w]), sl2, -off));
-                    const float p1 = ex2(fmaf(__uint_as_float(u[2 * w + 1]), sl2, -off));
-                    y0 += p0;
-                    y1 += p1;
-                    pw[w] = pack_bf16x2(p0, p1);
-                }
-                l = fmaf(l, a, y0 + y1);
-            } else {
-#pragma unroll
-                for (int w = 0; w < 32; w++) pw[w] = 0u;
-            }
-            tmem_st32(tP, pw);
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(b_p + 8 * bsel);
-        }
-        if (ok && nent > 0) ok = __all_sync(0xffffffffu, mbar_wait(b_o, 0, ctl));
-        tc_fence_after();
-        if (ok) {
-            const int qt = half ? qt1 : qt0;
-            int token = -1;
-            if (qt < p.nt) token = p.slot_src[qt * TE + (row & 63)];
-            const bool live = token >= 0;
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            const size_t orow = ((size_t)bh * p.seq + (live ? token : 0)) * kD;
-            const float* co = p.coarse + ((size_t)bh * p.nt + min(qt, p.nt - 1)) * kD;
-#pragma unroll 1
-            for (int q = 0; q < 4; q++) {
-                uint32_t o[32];
-                if (nent > 0) {
-                    tmem_ld32_issue(tO + 32u * q, o);
-                    tmem_ld_wait();
-                    tmem_pin(o);
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 32; c++) o[c] = 0u;
-                }
-                if (!live) continue;
-                float f[32];
-#pragma unroll
-                for (int c = 0; c < 8; c++) {
-                    const float4 cv = *reinterpret_cast<const float4*>(co + 32 * q + 4 * c);
-                    float g0 = 1.f, g1 = 1.f, g2 = 1.f, g3 = 1.f;
-                    if (p.gate) {
-                        const uint2 gw = *reinterpret_cast<const uint2*>(p.gate + orow + 32 * q + 4 * c);
-                        g0 = __uint_as_float(gw.x << 16);
-                        g1 = __uint_as_float(gw.x & 0xffff0000u);
-                        g2 = __uint_as_float(gw.y << 16);
-                        g3 = __uint_as_float(gw.y & 0xffff0000u);
-                    }
-                    f[4 * c] = __fadd_rn(__fmul_rn(cv.x, g0), __uint_as_float(o[4 * c]) * inv);
-                    f[4 * c + 1] = __fadd_rn(__fmul_rn(cv.y, g1), __uint_as_float(o[4 * c + 1]) * inv);
-                    f[4 * c + 2] = __fadd_rn(__fmul_rn(cv.z, g2), __uint_as_float(o[4 * c + 2]) * inv);
-                    f[4 * c + 3] = __fadd_rn(__fmul_rn(cv.w, g3), __uint_as_float(o[4 * c + 3]) * inv);
-                }
-                if (p.out_is_bf16) {
-                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.out) + orow + 32 * q);
-#pragma unroll
-                    for (int c = 0; c < 4; c++)
-                        dst[c] = make_uint4(pack_bf16x2(f[8 * c], f[8 * c + 1]), pack_bf16x2(f[8 * c + 2], f[8 * c + 3]),
-                                            pack_bf16x2(f[8 * c + 4], f[8 * c + 5]), pack_bf16x2(f[8 * c + 6], f[8 * c + 7]));
-                } else {
-                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + orow + 32 * q);
-#pragma unroll
-                    for (int c = 0; c < 8; c++) dst[c] = make_float4(f[4 * c], f[4 * c + 1], f[4 * c + 2], f[4 * c + 3]);
-                }
-            }
-        }
-        tc_fence_before();
-        asm volatile("bar.arrive 1, 160;" ::: "memory");
-        return;
-    }
-    if (warp == 4) {
-        // ------------------------------------------------------- TMA producer
-        if (lane == 0) {
-            WaitCtl ctl{abort_ptr, p.status, 11};
-            tma_prefetch_desc(&tk);
-            tma_prefetch_desc(&tv);
-            int idx = 0;
-            bool ok = true;
-            // Ring order = consumption order: K0 K1 V0 K2 V1 K3 ... (Q.K^T runs two steps ahead of P.V)
-            auto load = [&](int j, bool is_v) {
-                if (!ok) return;
-                const int tile = (int)(list[j] & 0xFFFFFu);
-                const int slot = idx % kFineNS, use = idx / kFineNS;
-                if (use > 0 && !mbar_wait(b_empty + 8 * slot, (use - 1) & 1, ctl)) { ok = false; return; }
-                const uint32_t dst = ring + slot * kKvTileB, bar = b_full + 8 * slot;
-                const CUtensorMap* map = is_v ? &tv : &tk;
-                mbar_expect_tx(bar, kKvTileB);
-                tma_load4(dst, map, bar, 0, tile * TE, bh, 0);
-                tma_load4(dst + kKvPanelB, map, bar, 64, tile * TE, bh, 0);
-                idx++;
-            };
-            if (nent > 0) load(0, false);
-            if (nent > 1) load(1, false);
-#pragma unroll 1
-            for (int j = 0; j < nent && ok; j++) {
-                load(j, true);
-                if (j + 2 < nent) load(j + 2, false);
-            }
-            mbar_wait(b_q, 0, ctl);
-            for (int s = 0; s < kFineNS && s < idx; s++) {
-                const int last = ((idx - 1 - s) / kFineNS) * kFineNS + s;
-                mbar_wait(b_full + 8 * s, (last / kFineNS) & 1, ctl);
-            }
-        }
-        return;
-    }
-    // --------------------------------------------------------- MMA issuer (warp 5)
-    if (lane == 0) {
-        WaitCtl ctl{abort_ptr, p.status, 12};
-        constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 64, 0);
-        constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 1);
-        bool ok = mbar_wait(b_q, 0, ctl);
-        tc_fence_after();
-        // ring index of K_j and V_j in the producer's order K0 K1 V0 K2 V1 ... V_{n-2} V_{n-1}
-        auto idx_k = [&](int j) { return j < 2 ? j : 2 * j - 1; };
-        auto idx_v = [&](int j) { return j == nent - 1 ? 2 * nent - 1 : 2 * j + 2; };
-        const uint64_t a0 = umma_desc_sw128(sQ, 16, 1024);
-        // S buffer (j & 1) = Q . K_j^T, then release K_j's slot
-        auto qk = [&](int j) -> bool {
-            const int ik = idx_k(j), slot = ik % kFineNS;
-            if (!mbar_wait(b_full + 8 * slot, (ik / kFineNS) & 1, ctl)) return false;
-            tc_fence_after();
-            const uint64_t b0 = umma_desc_sw128(ring + slot * kKvTileB, 16, 1024);
-            asm volatile(
-                "{\n\t.reg .pred pt, pf;\n\t.reg .b64 a, b;\n\t"
-                "setp.ne.b32 pf, %3, %3;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
-                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
-                "add.s64 a, %1, 2;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                "add.s64 a, %1, 4;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                "add.s64 a, %1, 6;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                "add.s64 a, %1, 1024;\n\tadd.s64 b, %2, 512;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                "add.s64 a, %1, 1026;\n\tadd.s64 b, %2, 514;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                "add.s64 a, %1, 1028;\n\tadd.s64 b, %2, 516;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                "add.s64 a, %1, 1030;\n\tadd.s64 b, %2, 518;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-                "}"
-                ::"r"(tbase + 64u * (uint32_t)(j & 1)), "l"(a0), "l"(b0), "r"(idesc_qk)
-                : "memory");
-            umma_commit(b_s + 8 * (j & 1));
-            umma_commit(b_empty + 8 * slot);
-            return true;
-        };
-        if (ok && nent > 0) ok = qk(0);
-        if (ok && nent > 1) ok = qk(1);
-#pragma unroll 1
-        for (int j = 0; j < nent && ok; j++) {
-            const int iv = idx_v(j), slotV = iv % kFineNS;
-            if (!mbar_wait(b_full + 8 * slotV, (iv / kFineNS) & 1, ctl)) { ok = false; break; }
-            if (!mbar_wait(b_p + 8 * (j & 1), (j >> 1) & 1, ctl)) { ok = false; break; }
-            tc_fence_after();
-            {
-                const uint64_t b0 = umma_desc_sw128(ring + slotV * kKvTileB, kKvPanelB, 1024);
-                asm volatile(
-                    "{\n\t.reg .pred pt, p0;\n\t.reg .b64 b;\n\t.reg .b32 t;\n\t"
-                    "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 pt, %3, %3;\n\t"
-                    "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
-                    "add.u32 t, %1, 8;\n\tadd.s64 b, %2, 128;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
-                    "add.u32 t, %1, 16;\n\tadd.s64 b, %2, 256;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
-                    "add.u32 t, %1, 24;\n\tadd.s64 b, %2, 384;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [t], b, %3, pt;\n\t"
-                    "}"
-                    ::"r"(tbase + 128u), "r"(tbase + 64u * (uint32_t)(j & 1)), "l"(b0), "r"(idesc_pv), "r"((uint32_t)(j > 0))
-                    : "memory");
-            }
-            umma_commit(b_od);
-            umma_commit(b_empty + 8 * slotV);
-            if (j == nent - 1) umma_commit(b_o);
-            if (j + 2 < nent) ok = qk(j + 2);  // into the buffer P.V_j just read (same thread: in order)
-        }
-        umma_commit(b_drain);
-        mbar_wait(b_drain, 0, ctl);
-    }
-    __syncwarp();
-    asm volatile("bar.sync 1, 160;" ::: "memory");
-    tc_fence_after();
-    tmem_dealloc(tbase, 256);
-#endif
-}
+// fv_vsa_fine_kernel: vsa_fine.cuh (included below, after this namespace's small kernels).
 
 static void host_tile_plan(Plan& pl) {
     const int t = pl.gt, h = pl.gh, w = pl.gw;
@@ -694,6 +329,8 @@ static Workspace carve(void* base, int bh, int nt, int topk) {
 }
 
 }  // namespace fvvsa
+
+#include "vsa_fine.cuh"
 
 using fvvsa::Plan;
 
@@ -831,7 +468,7 @@ extern "C" int fv_vsa_forward_bf16(void* stream_, void* plan, const void* q, con
     }
     FV_CUDA(cudaGetLastError());
 
-    fvvsa::FineParams fp{};
+    fvvsa::FineJob fp{};
     fp.selected = w.selected;
     fp.block_sizes = pl->d_block_sizes;
     fp.slot_src = pl->d_slot_src;
@@ -839,8 +476,8 @@ extern "C" int fv_vsa_forward_bf16(void* stream_, void* plan, const void* q, con
     fp.gate = (const bf*)gate;
     fp.out = out;
     fp.out_is_bf16 = out_is_bf16 ? 1 : 0;
-    fp.bh = bh;
-    fp.nt = nt;
+    fp.planes = bh;
+    fp.tiles = nt;
     fp.topk = topk;
     fp.seq = seq;
     fp.sl2 = scale * 1.4426950408889634f;
@@ -848,7 +485,7 @@ extern "C" int fv_vsa_forward_bf16(void* stream_, void* plan, const void* q, con
     rc = fvrt::status_word(dev, &fp.status);
     if (rc != FV_RAN) return rc;
     // shared memory: fixed part + union list + the two staged selections behind it
-    const size_t smem = 1024 + fvvsa::kQTileB + fvvsa::kFineNS * fvvsa::kKvTileB + 256 + 4 * ((size_t)fp.list_cap + 2 * (size_t)topk);
+    const size_t smem = fvvsa::FineSmem::bytes(fp.list_cap, topk);
     if (smem > 232448) return FV_DECLINED;
     CUtensorMap tq, tk, tv;
     const uint64_t dims[4] = {128, (uint64_t)nt * fvvsa::TE, (uint64_t)bh, 1};
