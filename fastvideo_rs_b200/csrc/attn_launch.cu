@@ -158,6 +158,10 @@ static int launch(cudaStream_t stream, const LaunchArgs& a) {
     int sms = 0;
     rc = fvrt::sm_count(dev, &sms);
     if (rc != FV_RAN) return rc;
+    // A persistent CTA holds its SM for the whole launch (168 registers x 384 threads are the SM's register file): a
+    // caller that runs a collective's copy kernels beside this launch asks for some SMs to stay free.
+    const int spare = fvrt::take_spare_sms();
+    if (spare > 0 && sms - spare >= 16) sms -= spare;
     const unsigned grid = (unsigned)(items < sms ? items : sms);
     fn<<<grid, kThreads, Smem::total, stream>>>(mq, mk, mv, jb);
     FV_CUDA(cudaGetLastError());

@@ -77,6 +77,14 @@ int sm_count(int device, int* out) {
     return FV_RAN;
 }
 
+// SMs the calling thread's NEXT attention launch leaves free (fv_hint_spare_sms); read and cleared by that launch.
+static thread_local int g_spare_sms = 0;
+int take_spare_sms() {
+    const int n = g_spare_sms;
+    g_spare_sms = 0;
+    return n;
+}
+
 static thread_local char g_last_kernel[256] = "";
 static bool g_logged[kLogKeys];
 
@@ -165,6 +173,13 @@ int encode_map4_cached(CUtensorMap* map, const void* base, const uint64_t dims[4
 }  // namespace fvrt
 
 extern "C" const char* fv_last_kernel(void) { return fvrt::g_last_kernel; }
+
+extern "C" int fv_hint_spare_sms(int sms) {
+    fvrt::clear_error();
+    if (sms < 0 || sms > 128) return fvrt::fail(FV_ERR_INVALID, "spare SMs: %d (0 .. 128)", sms);
+    fvrt::g_spare_sms = sms;
+    return FV_RAN;
+}
 extern "C" const char* fv_last_error(void) { return fvrt::g_err; }
 extern "C" const char* fv_version(void) { return "fvsdpa 0.1 (sm_100a)"; }
 

@@ -19,6 +19,8 @@ int require_sm100(int* device_out);
 int status_word(int device, int** ptr_out);
 // Number of SMs of `device` (cached).
 int sm_count(int device, int* out);
+// SMs the calling thread asked its next attention launch to leave free (fv_hint_spare_sms); cleared by the call.
+int take_spare_sms();
 // One line on stderr the first time `key` (a small integer per kernel kind) is seen in this
 // process, like the reference's rt::log::info_once one-liners that name the kernel a call ran
 // (crates/fastvideo-cudarc/src/rt/attn.rs:306-310).  FV_LOG=0 silences them.  The text of the last

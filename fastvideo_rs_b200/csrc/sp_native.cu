@@ -81,6 +81,7 @@ static int load_nccl() {
 
 struct Sp {
     int world = 1, rank = 0, seq = 0, bh = 0, groups = 1, bh_g = 0, dev = 0;
+    int spare_sms = 24;
     double op_timeout_s = 120.0;  // how long settle() polls a call the non-blocking communicator left in progress
     int start = 0, len = 0, seg_rows = 0;
     std::vector<int> starts, lens;
@@ -208,6 +209,9 @@ static int forward(Sp* s, cudaStream_t stream, const void* q, const void* k, con
         for (int g = 0; g < s->groups; g++) cudaStreamWaitEvent(stream, s->arrived[g], 0);
     };
     const int len1 = s->len, start1 = s->start;
+    // The gathers' copy kernels run beside pass 1: leave them SMs (FV_SP_SPARE_SMS, default 24), or the persistent
+    // attention CTAs that find no SM start when the gathers end and finish that much later.
+    if (s->world > 1) fv_hint_spare_sms(s->spare_sms);
     if (!any) {  // no row of this shard sees a key of another shard: pass 1 is the result
         rc = fv_sdpa_segments_bf16(stream, q, ks, vs, out, out_is_bf16, s->bh, s->len, 1, &len1, &start1, s->seg_rows, scale,
                                    mask_mode, bt, window, sink, s->start, nullptr, nullptr, nullptr);
@@ -353,6 +357,10 @@ static int create(const void* unique_id, int world, int rank, int seq, int bh, i
     rc = init_comm(s, id, world, rank, timeout_s);
     if (rc != FV_RAN) return bail(rc);
     if (timeout_s > 0) s->op_timeout_s = timeout_s;
+    if (const char* e = getenv("FV_SP_SPARE_SMS")) {
+        const int n = atoi(e);
+        if (n >= 0 && n <= 128) s->spare_sms = n;
+    }
     // Every rank must describe the same problem: a rank with another seq, bh or group count would size its
     // gathers differently and the first exchange would never complete.  One small all-gather settles it here,
     // where a mismatch is an error return on every rank instead of a hang later.

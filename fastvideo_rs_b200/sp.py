@@ -325,6 +325,9 @@ class SpAttention:
                 ev.record(self.comm_stream)
                 arrived = {src: ev for src in order}
         # pass 1: the local keys, while the exchange is in flight
+        if self.exchange == "nccl":
+            # the all-gather's copy kernels need SMs beside the persistent attention CTAs of pass 1
+            _lib.lib().fv_hint_spare_sms(int(os.environ.get("FV_SP_SPARE_SMS", "24")))
         l1, s1 = L.pass1()
         common = dict(causal=causal, q_row0=q_row0, q_split=q_split, q_row1=q_row1)
         if not order:  # no row of this rank sees a key of another rank: pass 1 is the result

@@ -66,6 +66,12 @@ FV_API int fv_device_status(void* stream, int* code_out);
  * (crates/fastvideo-cudarc/src/rt/attn.rs:306-310, rt/ops.rs:1385-1401). */
 FV_API const char* fv_last_kernel(void);
 
+/* The calling thread's NEXT attention launch (fv_sdpa_*, fv_sp_forward_bf16's passes are set by the handle itself)
+ * leaves `sms` SMs without a CTA.  The attention kernel is persistent and a CTA of it fills an SM: a collective whose
+ * copy kernels should run BESIDE the launch (an NCCL all-gather of the next keys under the pass over the local ones)
+ * otherwise waits for the launch to end, or makes part of its CTAs start late.  0 .. 128; one launch only. */
+FV_API int fv_hint_spare_sms(int sms);
+
 /* Failure-path self-test: launches ONE CTA of one warp that waits, with a budget of `cycles` clock cycles
  * (1e3 .. 2e9), on a barrier nobody arrives at.  The wait runs out, the kernel records status 109 and
  * returns normally; the next fv_device_status then answers FV_ERR_DEVICE_STATUS.  Nothing traps and the
