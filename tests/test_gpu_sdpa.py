@@ -381,3 +381,23 @@ def test_native_checker_passes(fvlib):
     exe = _build.build_native_checker()
     res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout[-2000:]
+
+
+def test_spare_sms_hint_shrinks_one_launch_and_changes_no_bit(fvlib, oracle):
+    """fv_hint_spare_sms: the next launch of the calling thread leaves SMs free (for a collective's copy kernels beside
+    it), the one after that uses every SM again; the work deal changes, the results do not."""
+    from fastvideo_rs_b200 import sdpa, _lib
+    q, k, v = qkv(oracle, 97, 24, 4096, 2048)
+    tq, tk, tv = to_dev_bf16(q), to_dev_bf16(k), to_dev_bf16(v)
+    full = sdpa.dense_fwd(tq, tk, tv)
+    line_full = _lib.last_kernel()
+    assert fvlib.fv_hint_spare_sms(24) == 0
+    fewer = sdpa.dense_fwd(tq, tk, tv)
+    line_fewer = _lib.last_kernel()
+    again = sdpa.dense_fwd(tq, tk, tv)
+    assert sdpa.device_status() == 0
+    import re
+    n_full, n_fewer, n_again = (int(re.search(r"(\d+) CTAs", s).group(1)) for s in (line_full, line_fewer, _lib.last_kernel()))
+    assert n_fewer == n_full - 24 and n_again == n_full
+    assert torch.equal(full, fewer) and torch.equal(full, again)
+    assert fvlib.fv_hint_spare_sms(-1) != 0 and fvlib.fv_hint_spare_sms(1000) != 0
