@@ -54,6 +54,8 @@
 //   FV_ATT_EARLY    keys of a tile whose P is handed to the issuer first (64 or 96), the rest follows; 128: P is
 //                   handed over whole (one wait and no pv_early commit per tile for the issuer)
 //   FV_ATT_SPLIT    TMEM map: 1 = S_A S_B O_A O_B, 0 = S_A O_A S_B O_B (no measurable difference)
+//   FV_ATT_WAIT_HINT  > 0: every barrier wait passes this many nanoseconds to mbarrier.try_wait as the longest
+//                   suspension before the thread looks again (0: the hardware's default)
 //   FV_ATT_BACKOFF  nanoseconds a waiting softmax thread sleeps between two probes of its barrier (0 = none);
 //                   FV_ATT_BACKOFF_LOADER the same for the loader thread
 #ifndef FV_ATT_POLY
@@ -64,6 +66,9 @@
 #endif
 #ifndef FV_ATT_SPLIT
 #define FV_ATT_SPLIT 1
+#endif
+#ifndef FV_ATT_WAIT_HINT
+#define FV_ATT_WAIT_HINT 0
 #endif
 #ifndef FV_ATT_BACKOFF
 #define FV_ATT_BACKOFF 0
@@ -344,11 +349,18 @@ struct Waiter {
     const Job& jb;
     uint32_t sbase;
     int role;
+    FV_DEV bool probe(uint32_t bar, uint32_t parity) const {
+#if FV_ATT_WAIT_HINT > 0
+        return mbar_try_hint(bar, parity, FV_ATT_WAIT_HINT) != 0u;
+#else
+        return mbar_try(bar, parity) != 0u;
+#endif
+    }
     FV_DEV bool operator()(uint32_t bar, uint32_t parity) const {
-        if (mbar_try(bar, parity)) return true;
+        if (probe(bar, parity)) return true;
         const long long t0 = clock64();
         uint32_t n = 0;
-        while (!mbar_try(bar, parity)) {
+        while (!probe(bar, parity)) {
             if (role == 1) {
                 if (FV_ATT_BACKOFF_LOADER > 0) __nanosleep(FV_ATT_BACKOFF_LOADER);
             } else if (role == 3) {

@@ -48,6 +48,19 @@ FV_DEV uint32_t mbar_try(uint32_t bar, uint32_t parity) {
     return ok;
 }
 
+// try_wait with an explicit limit (nanoseconds) on how long the thread may stay suspended before it looks again.
+FV_DEV uint32_t mbar_try_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok;
+}
+
 // Non-blocking probe of phase `parity` (test_wait never suspends the thread).
 FV_DEV uint32_t mbar_test(uint32_t bar, uint32_t parity) {
     uint32_t ok;
