@@ -49,3 +49,40 @@ def test_pointer_sequence_of_a_rolling_cache_and_errors(fvlib):
         KvSpec.rolling_window(10, 3, 3)
     g = KvSpec.global_window(1560)
     assert g.capacity == 32760 and not g.rolling
+
+
+def _plan_py(spec, global_end, local_end_prev, current_start, n):
+    """KvSpec::plan (wan/causal.rs:289-336) restated in plain Python; None where the reference returns an error."""
+    current_end = current_start + n
+    if not spec.rolling and current_end > spec.max_attention:
+        return None
+    if current_end < global_end and current_end + local_end_prev < global_end:
+        return None
+    advance = max(current_end - global_end, 0)
+    evicted = n + local_end_prev - spec.capacity if (spec.rolling and current_end > global_end and n + local_end_prev > spec.capacity) else 0
+    local_end = local_end_prev + advance - max(global_end - current_end, 0)
+    if local_end < 0 or local_end - evicted < 0:
+        return None
+    local_end -= evicted
+    if local_end < n or local_end > max(spec.capacity, n):
+        return None
+    return (evicted, local_end - n, local_end, max(local_end - spec.max_attention, 0))
+
+
+def test_plan_equals_its_restatement_on_random_states(fvlib):
+    import random
+    from fastvideo_rs_b200.wan import KvSpec
+    from fastvideo_rs_b200._lib import FvError
+    rng = random.Random(5)
+    for _ in range(3000):
+        ft = rng.choice([1, 2, 10, 78])
+        frames = rng.randint(1, 9)
+        spec = KvSpec(ft, frames * ft, rng.randint(0, frames - 1) * ft if frames > 1 else 0, rng.randint(1, frames) * ft, rng.random() < 0.7)
+        ge, le = rng.randint(0, 40 * ft), rng.randint(0, frames * ft)
+        cs, n = rng.randint(0, 40 * ft), rng.randint(0, 4 * ft)
+        want = _plan_py(spec, ge, le, cs, n)
+        try:
+            got = tuple(spec.plan(ge, le, cs, n))
+        except FvError:
+            got = None
+        assert got == want, (vars(spec), ge, le, cs, n, got, want)
