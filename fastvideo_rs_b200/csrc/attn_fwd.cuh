@@ -620,17 +620,21 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
                 cols.sink = min(row_span.sink - kt.k0, kt.valid);
                 cols.whole = (cols.lo <= 0 && cols.hi >= kKeyTile) || cols.sink >= kKeyTile;
             }
-            // The hot path takes whole tiles of rows that all have a reference (warp-uniform choice:
-            // everything below is warp-collective); the rest goes the careful way.
-            bool hot = seen > 0 && __all_sync(kFullWarp, cols.whole && rs.m != neg_inf());
+            // The hot path takes whole tiles (warp-uniform choice: everything below is warp-collective); tiles a
+            // mask or a segment's end cuts go the careful way.  A row without a reference yet (the first tile of
+            // an item, or a row that has only met invisible tiles so far: O and its sum are still zero) takes the
+            // maximum of its first 32 scores as one -- any reference is exact once O is divided by the row sum,
+            // and the guard below catches a row whose later scores outgrow it by 2^40.
+            bool hot = __all_sync(kFullWarp, cols.whole);
             if (hot) {
                 // Four 32-column chunks, the next one on its way from TMEM while this one's exponentials run.
                 uint32_t u0[32], u1[32], pw[64];
+                load_chunk(tS, 0, u0);
+                land_chunk(u0);
+                if (rs.m == neg_inf()) rs.m = max32(u0) * sl2;
                 const uint64_t s2 = pack_f32x2(sl2, sl2), nf = pack_f32x2(-rs.m, -rs.m);
                 uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
                 float top = 0.f;
-                load_chunk(tS, 0, u0);
-                land_chunk(u0);
                 if (tr) FV_TR(jb, tile, s_count - 1u, 1);
                 load_chunk(tS, 1, u1);
                 exp32<true>(u0, pw, s2, nf, acc0, acc1, top);
