@@ -33,11 +33,12 @@
 //   they come out of TMEM (the next chunk's load in flight), a quarter of the exponentials on the FMA
 //   pipe, and the row's sum of P is the proof that this was safe: every P is positive, so sum(P) <= 2^40
 //   implies max(P) <= 2^40, far inside what bf16 P and f32 accumulators hold, and a reference that lags
-//   the true maximum by any amount cancels exactly when O is divided by the row sum.  Only when a sum
-//   exceeds the guard (or the row has no reference yet: the first tile of an item) does the warp take the
-//   exact path: nothing of the tile has been stored, so it reads S again, takes the row maxima, moves the
-//   references, rescales O and the row sums, evaluates P again.  On N(0,1) inputs the exact path runs on
-//   the first tile of each item and nowhere else.
+//   the true maximum by any amount cancels exactly when O is divided by the row sum.  A row without a
+//   reference (the first tile of an item) takes the maximum of its first 32 scores as one.  Only when a sum
+//   exceeds the guard, or a mask or a segment's end cuts the tile, does the warp take the exact path:
+//   nothing of the tile has been stored, so it reads S again, takes the row maxima, moves the references,
+//   rescales O and the row sums, evaluates P again.  On N(0,1) inputs without a mask the exact path runs on
+//   ragged last tiles and nowhere else.
 // * Every wait is bounded: a role that gives up records a code in the status word, raises the CTA's
 //   abort flag, and every role falls through to the common exit, where copies in flight are awaited,
 //   the issuer's last MMA is awaited and TMEM is freed.  No trap, no endless spin.
