@@ -39,6 +39,13 @@
 //   nothing of the tile has been stored, so it reads S again, takes the row maxima, moves the references,
 //   rescales O and the row sums, evaluates P again.  On N(0,1) inputs without a mask the exact path runs on
 //   ragged last tiles and nowhere else.
+// * The item's output (write_item) is on the critical path of the next item -- the same warps run its
+//   first softmax -- and with few key tiles per item (cross-attention: 4) it is a third of the item.  It
+//   runs out of line (its registers are not the hot loop's), loads O from TMEM in two alternating
+//   32-column buffers, transposes 16-byte pieces between neighbouring lanes so that a warp's store covers
+//   whole 64- or 128-byte runs of 8 or 4 rows instead of 16 bytes of 32 rows, and the softmax warp looks
+//   up its next item before it waits for the last product, not after the output.  Together 14 % of the
+//   item at 4 key tiles (20 300 -> 17 400 cycles), nothing at 256 and more.
 // * Every wait is bounded: a role that gives up records a code in the status word, raises the CTA's
 //   abort flag, and every role falls through to the common exit, where copies in flight are awaited,
 //   the issuer's last MMA is awaited and TMEM is freed.  No trap, no endless spin.
@@ -547,8 +554,50 @@ static __device__ __noinline__ void careful_tile(uint32_t tS, uint32_t tO, uint3
 }
 
 // 32 columns of one output row: O / l (+ the earlier pass' share), to bf16 or f32.
-FV_DEV void store_cols32(const Job& jb, const uint32_t (&o)[32], float inv, float prev_w, const float* prev_row,
-                         void* out_row) {
+// A thread holds 32 columns of ITS row; stored as they are, a warp's 16-byte stores would touch 32 rows (32
+// lines) each, and the store path takes about a cycle per line and instruction: 8 000 cycles per item for both
+// row tiles, which items of a few key tiles (cross-attention) cannot hide.  So the 16-byte pieces are first
+// transposed inside groups of G lanes (G = pieces per row: 4 for bf16, 8 for f32): afterwards piece k of a lane
+// is piece (lane % G) of the row of lane k of its group, and store number k of a warp writes 32 / G rows' whole
+// 64- or 128-byte runs.
+template <int G>
+FV_DEV void transpose_pieces(uint4 (&p)[G], int lane) {
+#pragma unroll
+    for (int d = G / 2; d > 0; d >>= 1) {
+        const bool hi = (lane & d) != 0;
+#pragma unroll
+        for (int i = 0; i < G; i++) {
+            if (i & d) continue;
+            const uint4 send = hi ? p[i] : p[i | d];
+            uint4 recv;
+            recv.x = __shfl_xor_sync(kFullWarp, send.x, d);
+            recv.y = __shfl_xor_sync(kFullWarp, send.y, d);
+            recv.z = __shfl_xor_sync(kFullWarp, send.z, d);
+            recv.w = __shfl_xor_sync(kFullWarp, send.w, d);
+            if (hi) p[i] = recv;
+            else p[i | d] = recv;
+        }
+    }
+}
+
+// Where the rows of an item's plane go: element offset of row r is plane_el + r * row_stride (BHSD, or the
+// merged-heads [b, s, h * d] layout).
+struct OutRows {
+    size_t plane_el;
+    size_t row_stride;
+};
+// What the item's output stage needs of the job, by value (it runs out of line).
+struct OutJob {
+    void* out;
+    const float* prev_o;
+    const float* prev_lse;
+    float* lse_out;
+    int sq, out_heads, out_is_bf16;
+};
+
+// Columns [32 q, 32 q + 32) of the warp's 32 rows (lane = row qr; rows at or past sq are not stored).  Warp-collective.
+FV_DEV void store_cols32(const OutJob& jb, const uint32_t (&o)[32], float inv, float prev_w, const float* prev_row,
+                         const OutRows& rows, int q, int qr, int lane) {
     float f[32];
 #pragma unroll
     for (int c = 0; c < 32; c++) f[c] = as_f(o[c]) * inv;
@@ -564,16 +613,97 @@ FV_DEV void store_cols32(const Job& jb, const uint32_t (&o)[32], float inv, floa
         }
     }
     if (jb.out_is_bf16) {
-        uint4* dst = reinterpret_cast<uint4*>(out_row);
+        uint4 p[4];
 #pragma unroll
         for (int c = 0; c < 4; c++)
-            dst[c] = make_uint4(pack_bf16x2(f[8 * c], f[8 * c + 1]), pack_bf16x2(f[8 * c + 2], f[8 * c + 3]),
-                                pack_bf16x2(f[8 * c + 4], f[8 * c + 5]), pack_bf16x2(f[8 * c + 6], f[8 * c + 7]));
-    } else {
-        float4* dst = reinterpret_cast<float4*>(out_row);
+            p[c] = make_uint4(pack_bf16x2(f[8 * c], f[8 * c + 1]), pack_bf16x2(f[8 * c + 2], f[8 * c + 3]),
+                              pack_bf16x2(f[8 * c + 4], f[8 * c + 5]), pack_bf16x2(f[8 * c + 6], f[8 * c + 7]));
+        transpose_pieces<4>(p, lane);
+        const int l = lane & 3;
+        unsigned short* base = reinterpret_cast<unsigned short*>(jb.out) + rows.plane_el + 32 * q + 8 * l;
 #pragma unroll
-        for (int c = 0; c < 8; c++) dst[c] = make_float4(f[4 * c], f[4 * c + 1], f[4 * c + 2], f[4 * c + 3]);
+        for (int k = 0; k < 4; k++) {
+            const int r = qr - l + k;
+            if (r < jb.sq) *reinterpret_cast<uint4*>(base + (size_t)r * rows.row_stride) = p[k];
+        }
+    } else {
+        uint4 p[8];
+#pragma unroll
+        for (int c = 0; c < 8; c++)
+            p[c] = make_uint4(__float_as_uint(f[4 * c]), __float_as_uint(f[4 * c + 1]), __float_as_uint(f[4 * c + 2]),
+                              __float_as_uint(f[4 * c + 3]));
+        transpose_pieces<8>(p, lane);
+        const int l = lane & 7;
+        float* base = reinterpret_cast<float*>(jb.out) + rows.plane_el + 32 * q + 4 * l;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int r = qr - l + k;
+            if (r < jb.sq) *reinterpret_cast<uint4*>(base + (size_t)r * rows.row_stride) = p[k];
+        }
     }
+}
+
+// The item's output: O / row sum (merged with an earlier pass' row where there is one), the row's log-sum-exp.
+// Out of line like careful_tile: it runs once per item, and inlined its registers (two 32-column buffers, the
+// transposed pieces) would be allocated against the hot loop's.  Warp-collective.
+static __device__ __noinline__ void write_item(const Job& job, const OutJob jb, uint32_t tO, int plane, int qr, float m_in, float l_in, bool have_o,
+                int lane, int tile, uint32_t step, bool stamp) {
+    const bool live = qr < jb.sq;  // rows past sq only take part in the warp-collective TMEM loads
+    const float m = m_in, l = l_in;
+    float inv = l > 0.f ? 1.f / l : 0.f;
+    const float lse = (l > 0.f && (jb.lse_out || jb.prev_o)) ? m + log2f(l) : neg_inf();  // (only where it is written or merged)
+    const size_t rowi = (size_t)plane * jb.sq + (live ? qr : 0);
+    float prev_w = 0.f;
+    if (live) {
+        if (jb.prev_o) {
+            const float pl = jb.prev_lse[rowi];
+            const float top = fmaxf(lse, pl);
+            float lse_all = neg_inf();
+            if (top != neg_inf()) {
+                const float wn = exp2f(lse - top), wp = exp2f(pl - top);
+                const float den = 1.f / (wn + wp);
+                inv *= wn * den;
+                prev_w = wp * den;
+                lse_all = top + log2f(wn + wp);
+            }
+            if (jb.lse_out) jb.lse_out[rowi] = lse_all;
+        } else if (jb.lse_out) {
+            jb.lse_out[rowi] = lse;
+        }
+    }
+    OutRows rows{(size_t)plane * jb.sq * kD, (size_t)kD};
+    if (jb.out_heads > 0) {
+        const int bb = plane / jb.out_heads, hh = plane - bb * jb.out_heads;
+        rows.plane_el = ((size_t)bb * jb.sq * jb.out_heads + hh) * kD;
+        rows.row_stride = (size_t)jb.out_heads * kD;
+    }
+    const float* prev_row = (live && jb.prev_o) ? jb.prev_o + rowi * kD : nullptr;  // (the earlier pass is BHSD)
+    // Two buffers: the next 32 columns are on their way from TMEM while these are scaled and stored.
+    uint32_t oa[32], ob[32];
+    if (have_o) {  // warp-uniform
+        tmem_ld32_issue(tO, oa);
+    } else {
+#pragma unroll
+        for (int c = 0; c < 32; c++) oa[c] = ob[c] = 0u;
+    }
+#pragma unroll 1
+    for (int h = 0; h < 2; h++) {
+        if (have_o) {
+            tmem_ld_wait();
+            tmem_pin(oa);
+            tmem_ld32_issue(tO + 32u * (2 * h + 1), ob);
+        }
+        store_cols32(jb, oa, inv, prev_w, prev_row ? prev_row + 32 * (2 * h) : nullptr, rows, 2 * h, qr, lane);
+        if (h == 0 && stamp && have_o) FV_TR(job, tile, step, 4);
+        if (have_o) {
+            tmem_ld_wait();
+            tmem_pin(ob);
+            if (h == 0) tmem_ld32_issue(tO + 64u, oa);
+        }
+        store_cols32(jb, ob, inv, prev_w, prev_row ? prev_row + 32 * (2 * h + 1) : nullptr, rows, 2 * h + 1, qr, lane);
+        if (h == 0 && stamp && have_o) FV_TR(job, tile, step, 5);
+    }
+    if (stamp && have_o) FV_TR(job, tile, step, 7);
 }
 
 template <bool MASKED>
@@ -588,8 +718,9 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
     uint32_t s_count = 0, o_count = 0;
 
     Deal deal;
-    for (int i = deal.next(jb); i >= 0; i = deal.next(jb)) {
-        const Item it = item_at(jb, i);
+    int i = deal.next(jb);
+    Item it = item_at(jb, max(i, 0));
+    while (i >= 0) {
         const int qr = it.q0 + kRowTile * tile + row;  // this thread's row inside the plane
         const Span cta_span = span_of<MASKED>(jb, global_row(jb, it.q0), global_row(jb, min(it.q0 + kItemRows, jb.sq) - 1));
         const Span row_span = span_of<MASKED>(jb, global_row(jb, qr), global_row(jb, qr));
@@ -692,56 +823,18 @@ FV_DEV void softmax_warp(const Job& jb, uint32_t sbase, uint32_t tmem, int warp,
         }
 
         // ------------------------------------------------------------------------- the item's output
+        // (the next item is looked up now, while the last product runs, not after the output is written)
+        const int plane = it.plane;
+        i = deal.next(jb);
+        if (i >= 0) it = item_at(jb, i);
         if (seen > 0) {
             if (!__all_sync(kFullWarp, wait(bt + Smem::o_ready, o_count & 1u))) return;
             o_count++;
             tc_fence_after();
+            if (quad == 0 && lane == 0) FV_TR(jb, tile, s_count - 1u, 3);
         }
-        const bool live = qr < jb.sq;  // rows past sq only take part in the warp-collective TMEM loads
-        const float m = rs.m, l = rs.l;
-        float inv = l > 0.f ? 1.f / l : 0.f;
-        const float lse = l > 0.f ? m + log2f(l) : neg_inf();
-        const size_t rowi = (size_t)it.plane * jb.sq + (live ? qr : 0);
-        float prev_w = 0.f;
-        if (live) {
-            if (jb.prev_o) {
-                const float pl = jb.prev_lse[rowi];
-                const float top = fmaxf(lse, pl);
-                float lse_all = neg_inf();
-                if (top != neg_inf()) {
-                    const float wn = exp2f(lse - top), wp = exp2f(pl - top);
-                    const float den = 1.f / (wn + wp);
-                    inv *= wn * den;
-                    prev_w = wp * den;
-                    lse_all = top + log2f(wn + wp);
-                }
-                if (jb.lse_out) jb.lse_out[rowi] = lse_all;
-            } else if (jb.lse_out) {
-                jb.lse_out[rowi] = lse;
-            }
-        }
-        size_t out_el = rowi * kD;  // BHSD element offset of the row (also the earlier pass' layout)
-        const size_t prev_el = out_el;
-        if (jb.out_heads > 0) {
-            const int bb = it.plane / jb.out_heads, hh = it.plane - bb * jb.out_heads;
-            out_el = (((size_t)bb * jb.sq + (live ? qr : 0)) * jb.out_heads + hh) * kD;
-        }
-#pragma unroll 1
-        for (int q = 0; q < 4; q++) {
-            uint32_t o[32];
-            if (seen > 0) {  // warp-uniform
-                tmem_ld32_issue(tO + 32u * q, o);
-                tmem_ld_wait();
-                tmem_pin(o);
-            } else {
-#pragma unroll
-                for (int c = 0; c < 32; c++) o[c] = 0u;
-            }
-            if (!live) continue;
-            void* dst = jb.out_is_bf16 ? (void*)(reinterpret_cast<unsigned short*>(jb.out) + out_el + 32 * q)
-                                       : (void*)(reinterpret_cast<float*>(jb.out) + out_el + 32 * q);
-            store_cols32(jb, o, inv, prev_w, jb.prev_o ? jb.prev_o + prev_el + 32 * q : nullptr, dst);
-        }
+        write_item(jb, OutJob{jb.out, jb.prev_o, jb.prev_lse, jb.lse_out, jb.sq, jb.out_heads, jb.out_is_bf16}, tO, plane, qr,
+                   rs.m, rs.l, seen > 0, lane, tile, s_count - 1u, quad == 0 && lane == 0);
         // The next item's first P.V overwrites O.  The issuer issues it only after all four warps of the
         // row tile have arrived at p_ready for that item's first key tile, and a warp gets there only
         // after its loads above have completed.
