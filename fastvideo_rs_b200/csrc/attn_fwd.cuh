@@ -44,8 +44,8 @@
 //   runs out of line (its registers are not the hot loop's), loads O from TMEM in two alternating
 //   32-column buffers, transposes 16-byte pieces between neighbouring lanes so that a warp's store covers
 //   whole 64- or 128-byte runs of 8 or 4 rows instead of 16 bytes of 32 rows, and the softmax warp looks
-//   up its next item before it waits for the last product, not after the output.  Together 14 % of the
-//   item at 4 key tiles (20 300 -> 17 400 cycles), nothing at 256 and more.
+//   up its next item before it waits for the last product, not after the output.  Together 12 % of the
+//   item at 4 key tiles (20 300 -> 17 800 cycles), nothing at 256 and more.
 // * Every wait is bounded: a role that gives up records a code in the status word, raises the CTA's
 //   abort flag, and every role falls through to the common exit, where copies in flight are awaited,
 //   the issuer's last MMA is awaited and TMEM is freed.  No trap, no endless spin.
