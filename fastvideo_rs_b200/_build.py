@@ -62,7 +62,7 @@ def build_native_checker() -> Path:
     out = src.with_suffix(".bin")
     if out.exists() and out.stat().st_mtime > max(src.stat().st_mtime, LIB.stat().st_mtime):
         return out
-    cmd = [nvcc_path(), *ARCH_FLAGS, "-O2", "-std=c++17", "-o", str(out), str(src), f"-L{PKG}", "-lfvsdpa",
+    cmd = [nvcc_path(), *ARCH_FLAGS, "-O2", "-std=c++17", "-o", str(out), str(src), f"-L{PKG}", "-lfvsdpa", "-ldl",
            "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../fastvideo_rs_b200"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:

@@ -3,7 +3,16 @@
 // same bf16 inputs, and times each case with CUDA events.  No torch, no
 // Python: it exists so that a kernel change can be checked in seconds.
 //
-//   sdpa_check [--bench] [--selftest] [--case bh,sq,sk[,block_tokens,window,sink]]...
+//   sdpa_check [--bench] [--selftest] [--trace STEPS] [--case bh,sq,sk[,block_tokens,window,sink]]...
+//
+// --trace STEPS: with a library built with -DFV_ATT_TRACE (a bring-up build, never the shipped one) every case
+// is launched three times and the SM-clock stamps CTA 0 wrote during the last launch are printed, one line per
+// role (smA / smB: lane 0 of the first softmax warp of row tile A / B; iss: the issuer) and key step:
+//   smA/smB  0 S complete seen, 1 first 32 columns loaded, 2 exponentials done, 6 P handed over; on the last
+//            step of an item also 3 last product seen, 4 / 5 first / second 32 columns of the output stored,
+//            7 output stored
+//   iss      0 K/V pair arrived, 2 / 5 P of tile A / B seen, 3 / 6 Q.K^T of tile A / B issued
+// (cycles since the first stamp, -1 = not stamped).  Without such a build the option reports that and fails.
 //
 // --selftest also drives the bounded-wait failure path (fv_selftest_wait_timeout) and checks that
 // fv_device_status reports it once and that a normal case runs afterwards.
@@ -11,6 +20,7 @@
 // Exit code 0 when every case is within tolerance (max-abs 2e-2, mean-abs
 // 2e-3 against the f64 evaluation) and no kernel reported a status.
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 #include <math.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -228,6 +238,68 @@ static int run_case(const Case& c, bool bench, int out_bf16) {
     return pass ? 0 : 1;
 }
 
+// The stamps of one launch of a bring-up build (see the header).
+static int trace_case(const Case& c, int steps) {
+    typedef void (*set_trace_fn)(unsigned long long*, int);
+    set_trace_fn set_trace = (set_trace_fn)dlsym(RTLD_DEFAULT, "fv_debug_set_trace");
+    if (!set_trace) {
+        printf("--trace: this libfvsdpa.so was built without -DFV_ATT_TRACE\n");
+        return 1;
+    }
+    const size_t nq = (size_t)c.bh * c.sq * 128, nk = (size_t)c.bh * c.sk * 128;
+    Rng r(7);
+    std::vector<uint16_t> q(nq), k(nk), v(nk);
+    fill_normal(q, r);
+    fill_normal(k, r);
+    fill_normal(v, r);
+    void *dq, *dk, *dv, *dout;
+    unsigned long long* dtr;
+    const size_t tn = (size_t)4 * steps * 8;
+    CK(cudaMalloc(&dq, nq * 2));
+    CK(cudaMalloc(&dk, nk * 2));
+    CK(cudaMalloc(&dv, nk * 2));
+    CK(cudaMalloc(&dout, nq * 2));
+    CK(cudaMalloc(&dtr, tn * 8));
+    CK(cudaMemcpy(dq, q.data(), nq * 2, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(dk, k.data(), nk * 2, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(dv, v.data(), nk * 2, cudaMemcpyHostToDevice));
+    const float scale = 1.f / sqrtf(128.f);
+    for (int rep = 0; rep < 3; rep++) {
+        CK(cudaMemset(dtr, 0, tn * 8));
+        set_trace(rep == 2 ? dtr : nullptr, steps);
+        const int rc = fv_sdpa_dense_bf16(nullptr, dq, dk, dv, dout, 1, c.bh, c.sq, c.sk, 128, scale,
+                                          c.bt > 0 ? FV_MASK_BLOCK_CAUSAL : FV_MASK_NONE, c.bt, c.win, c.sink, 0);
+        if (rc != FV_RAN) {
+            printf("--trace: rc=%d %s\n", rc, fv_last_error());
+            return 1;
+        }
+        CK(cudaDeviceSynchronize());
+    }
+    set_trace(nullptr, 0);
+    std::vector<unsigned long long> t(tn);
+    CK(cudaMemcpy(t.data(), dtr, tn * 8, cudaMemcpyDeviceToHost));
+    unsigned long long t0 = ~0ull;
+    for (unsigned long long x : t)
+        if (x && x < t0) t0 = x;
+    const char* names[3] = {"smA", "smB", "iss"};
+    printf("# trace bh%d sq%d sk%d bt%d: role step ev0 .. ev7\n", c.bh, c.sq, c.sk, c.bt);
+    for (int s = 0; s < steps; s++)
+        for (int role = 0; role < 3; role++) {
+            printf("%s %3d:", names[role], s);
+            for (int e = 0; e < 8; e++) {
+                const unsigned long long x = t[((size_t)role * steps + s) * 8 + e];
+                printf(" %8lld", x ? (long long)(x - t0) : -1ll);
+            }
+            printf("\n");
+        }
+    cudaFree(dq);
+    cudaFree(dk);
+    cudaFree(dv);
+    cudaFree(dout);
+    cudaFree(dtr);
+    return 0;
+}
+
 static int selftest() {
     int rc = fv_selftest_wait_timeout(nullptr, 2000000);
     if (rc != FV_RAN) {
@@ -252,10 +324,12 @@ static int selftest() {
 
 int main(int argc, char** argv) {
     bool bench = false, st = false;
+    int trace_steps = 0;
     std::vector<Case> cases;
     for (int i = 1; i < argc; i++) {
         if (!strcmp(argv[i], "--bench")) bench = true;
         else if (!strcmp(argv[i], "--selftest")) st = true;
+        else if (!strcmp(argv[i], "--trace") && i + 1 < argc) trace_steps = atoi(argv[++i]);
         else if (!strcmp(argv[i], "--case") && i + 1 < argc) {
             Case c{1, 1, 1, 0, 0, 0};
             sscanf(argv[++i], "%d,%d,%d,%d,%d,%d", &c.bh, &c.sq, &c.sk, &c.bt, &c.win, &c.sink);
@@ -275,6 +349,10 @@ int main(int argc, char** argv) {
         for (const Case& c : def) cases.push_back(c);
     }
     int bad = 0;
+    if (trace_steps > 0) {
+        for (const Case& c : cases) bad += trace_case(c, trace_steps);
+        return bad ? 1 : 0;
+    }
     for (const Case& c : cases) {
         bad += run_case(c, bench, 1);
     }
